@@ -6,7 +6,7 @@ continuous-batching scheduler and hand-written CUDA kernels.
     engine = cb.Engine("model_dir", dtype="bfloat16")
     outputs = engine.generate([[1, 2, 3]], cb.SamplingParams(max_new_tokens=16))
 """
-from .config import (ConfigError, GPT2Config, LayerSpec, ModelSpec, PartSpec, config_from_dict,
+from .config import (ConfigError, GPT2Config, LayerSpec, ModelSpec, PartSpec, VekedraConfig, config_from_dict,
                      known_architectures, load_config, register_architecture)
 from .weights import InitScheme, WeightsError, write_model_folder
 

@@ -10,7 +10,7 @@ src/paged_kv_cache.cpp:8-14 - here a group is one allocation).  The host bookkee
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -48,12 +48,22 @@ class CacheGroup:
         return len(self.layers) * self.need.elements_per_token() * self.page_size * itemsize
 
 
+def _need_with_readers(model, li: int, need: CacheNeed) -> CacheNeed:
+    """A layer's pages stay as long as the layer itself OR a layer that reads its cache can reach them: the
+    window that decides when pages go back is the widest of theirs (0, no window, is the widest of all)."""
+    windows = [need.window] + [int(getattr(other.mixer, "window", 0)) for other in model.layers
+                               if other.spec.cache_source == li]
+    widest = 0 if any(w <= 0 for w in windows) else max(windows)
+    return need if widest == need.window else replace(need, window=widest)
+
+
 def cache_groups_of(model, page_size: int) -> List[CacheGroup]:
     groups: List[CacheGroup] = []
     for li, layer in enumerate(model.layers):
         need = layer.mixer.cache_need()
         if need is None or layer.spec.cache_source is not None:
             continue
+        need = _need_with_readers(model, li, need)
         for g in groups:
             if g.need == need:
                 g.layers.append(li)

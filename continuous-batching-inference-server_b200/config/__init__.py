@@ -2,9 +2,11 @@ from .spec import ConfigError, LayerSpec, ModelSpec, PartSpec
 from .registry import (architecture_name, config_from_dict, known_architectures, load_config,
                        register_architecture)
 from .gpt2 import GPT2Config
+from .vekedra import VekedraConfig
 
 for _name in ("GPT2LMHeadModel", "TinyGPT", "gpt2"):
     register_architecture(_name, GPT2Config)
+register_architecture("Vekedra", VekedraConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "GPT2Config", "architecture_name",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "GPT2Config", "VekedraConfig", "architecture_name",
            "config_from_dict", "known_architectures", "load_config", "register_architecture"]

@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to what builds it.
 
-``config.json`` names its architecture (``architectures[0]``, else ``model_type``);
+``config.json`` names its architecture (``architectures[0]``, else ``architecture``, else ``model_type``);
 the registry maps that name to the typed configuration class, whose
 ``model_spec()`` lists the parts of every layer.  The reference has one
 hard-wired model (src/transformer.cpp:44-99) and no names.
@@ -26,9 +26,9 @@ def known_architectures():
 
 
 def architecture_name(d: Dict[str, Any]) -> str:
-    name = (d.get("architectures") or [None])[0] or d.get("model_type")
+    name = (d.get("architectures") or [None])[0] or d.get("architecture") or d.get("model_type")
     if not name:
-        raise ConfigError("config.json names no architecture ('architectures' or 'model_type'); "
+        raise ConfigError("config.json names no architecture ('architectures', 'architecture' or 'model_type'); "
                           f"known: {known_architectures()}")
     return str(name)
 

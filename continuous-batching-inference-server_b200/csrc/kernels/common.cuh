@@ -20,6 +20,8 @@
 #define CBIS_ACT_NONE 0
 #define CBIS_ACT_GELU_ERF 1
 #define CBIS_ACT_GELU_TANH 2
+#define CBIS_ACT_SILU 3
+#define CBIS_ACT_SIGMOID 4
 
 #define CBIS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -125,8 +127,12 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[32];
 }
 
-// GELU in 32-bit.  erf form: kernels/elementwise.cu:59-66 of the reference; tanh form: GPT-2's gelu_new.
+// Activations in 32-bit.  GELU, erf form: kernels/elementwise.cu:59-66 of the reference; tanh form: GPT-2's gelu_new;
+// silu(v) = v * sigmoid(v); sigmoid alone is the activation of a gate.
+__device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float activate(float v, int act) {
+  if (act == CBIS_ACT_SILU) return v * sigmoid_f32(v);
+  if (act == CBIS_ACT_SIGMOID) return sigmoid_f32(v);
   if (act == CBIS_ACT_GELU_ERF) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
   if (act == CBIS_ACT_GELU_TANH) {
     const float c = 0.7978845608028654f;  // sqrt(2/pi)

@@ -8,6 +8,7 @@ random weights of that configuration, ``Engine(folder)`` loads a model folder, a
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 from dataclasses import dataclass
@@ -36,7 +37,8 @@ class Engine:
     def __init__(self, model: Union[str, Model], *, dtype="bfloat16", page_size: int = 16,
                  num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_num_seqs: int = 16,
                  max_batched_tokens: int = 512, prefill_chunk: Optional[int] = None,
-                 memory_fraction: float = 0.85, device: str = "cuda", poison_freed_pages: Optional[bool] = None):
+                 memory_fraction: float = 0.85, device: str = "cuda", poison_freed_pages: Optional[bool] = None,
+                 max_model_len: Optional[int] = None):
         """``model``: a folder with config.json and model.safetensors, or a loaded ``Model``.
         Engine options in the reference's terms: ``page_size`` = kPageSize (include/config.hpp:20),
         ``num_pages`` = kMaxPages, ``max_num_seqs`` = kMaxSlots, ``max_batched_tokens`` =
@@ -44,10 +46,21 @@ class Engine:
         (src/bench_tiering.cpp:78 uses 512); default: the token budget.  ``poison_freed_pages`` (default:
         the environment's CBIS_POISON_FREED_PAGES=1) is a debugging mode: every page that a request gives back
         is filled with NaN before the next step runs, so a read of a page that is no longer held, or of a
-        token slot beyond a request's length in a page that was used before, shows as NaN logits."""
+        token slot beyond a request's length in a page that was used before, shows as NaN logits.
+        ``max_model_len``: the longest request the engine takes (block tables are sized for it); at most the model's
+        own position limit; for a model without one the default is what the pool is asked to hold (``num_pages`` or
+        ``max_tokens``), else 32,768."""
         if not torch.cuda.is_available():
             raise RuntimeError("the engine needs a CUDA device (sm_100a); there is no CPU path")
         self.model = load_model(model, dtype, device) if isinstance(model, str) else model
+        own_limit = int(self.model.spec.max_positions)
+        if max_model_len is not None and int(max_model_len) <= 0:
+            raise ValueError("max_model_len must be positive")
+        if own_limit <= 0:      # the architecture sets no limit: the engine's holds
+            asked = num_pages * page_size if num_pages else max_tokens
+            self.model.spec = dataclasses.replace(self.model.spec, max_positions=int(max_model_len or asked or 32768))
+        elif max_model_len is not None and int(max_model_len) < own_limit:
+            self.model.spec = dataclasses.replace(self.model.spec, max_positions=int(max_model_len))
         self.pool = CachePool(self.model, page_size=page_size, num_pages=num_pages, max_tokens=max_tokens,
                               max_requests=max_num_seqs, memory_fraction=memory_fraction, device=device)
         self.runner = ModelRunner(self.model, self.pool, max_batched_tokens=max_batched_tokens,

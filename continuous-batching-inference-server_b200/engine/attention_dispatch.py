@@ -47,7 +47,12 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
     nd = ctx.n_decode
     T = ctx.n_rows
     hd, ps = mixer.head_dim, cache.page_size
-    k_off, v_off = mixer.d_q, mixer.d_q + mixer.d_kv
+    # the pages that stand for keys and for values: "k" and "v", or what the mixer names (a mixer whose keys and
+    # values are both one cached array names it twice)
+    k_name, v_name = getattr(mixer, "kv_arrays", ("k", "v"))
+    k_pages, v_pages = cache.arrays[k_name], cache.arrays[v_name]
+    k_off = mixer.d_q
+    v_off = k_off if v_name == k_name else k_off + mixer.d_kv      # one array for both: one column block for both
     fast_decode = qkv.dtype == torch.bfloat16 and hd % 8 == 0 and hd <= 256 and nd > 0
     first_general = nd if fast_decode else 0
     if fast_decode:
@@ -57,24 +62,24 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
         if nsplit > 1:
             scratch, counters = ctx.decode_scratch(ops.decode_scratch_floats(nd, mixer.n_head, hd, nsplit),
                                                    nd * mixer.n_head)
-        ops.paged_decode_bf16(qkv[:nd], k_off if mixer.own_kv else -1, v_off if mixer.own_kv else -1, cache.k, cache.v,
+        ops.paged_decode_bf16(qkv[:nd], k_off if mixer.own_kv else -1, v_off if mixer.own_kv else -1, k_pages, v_pages,
                               view.block_table, ctx.row_seq, ctx.positions, view.slot_mapping, out[:nd], scratch, counters,
                               mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale, mixer.window, nsplit)
     if first_general < T:
         r = slice(first_general, T)
         if mixer.own_kv:
-            ops.kv_write(qkv[r], k_off, v_off, cache.k, cache.v, view.slot_mapping[r], mixer.n_kv_head, hd, ps)
+            ops.kv_write(qkv[r], k_off, v_off, k_pages, v_pages, view.slot_mapping[r], mixer.n_kv_head, hd, ps)
         tiled = qkv.dtype == torch.bfloat16 and ps & (ps - 1) == 0 and first_general == nd
         if tiled and hd in (64, 128) and 8 <= ps <= 128 and ops.USE_TCGEN05:
             # TMA + tcgen05: q and out keep their full row numbering, the kernel finds its rows through cu_rows
             chunks, partial = _key_chunks(ctx, mixer, nd, T, hd, row_tile=128, blocks_per_tile=2, blocks_per_sm=2, min_chunk=8192)
-            ops.paged_prefill_tc5(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
+            ops.paged_prefill_tc5(qkv, k_pages, v_pages, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                   ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                   mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
         if tiled and hd % 16 == 0 and 16 <= hd <= 128:
             chunks, partial = _key_chunks(ctx, mixer, nd, T, hd)
-            ops.paged_prefill_bf16(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
+            ops.paged_prefill_bf16(qkv, k_pages, v_pages, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                    ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                    mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
@@ -83,16 +88,16 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
             if nd > 0:
                 d = slice(0, nd)
                 chunks, partial = _general_chunks(ctx, mixer, nd, hd)
-                ops.paged_attention_generic(qkv[d, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[d],
+                ops.paged_attention_generic(qkv[d, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq[d],
                                             ctx.positions[d], out[d], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
                                             mixer.window, chunks, partial)
             if ctx.n_segments > nd:
                 chunks, partial = _key_chunks(ctx, mixer, nd, T, hd)
-                ops.paged_prefill_f32(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
+                ops.paged_prefill_f32(qkv, k_pages, v_pages, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                       ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                       mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
         chunks, partial = _general_chunks(ctx, mixer, T - first_general, hd)
-        ops.paged_attention_generic(qkv[r, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[r],
+        ops.paged_attention_generic(qkv[r, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq[r],
                                     ctx.positions[r], out[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
                                     mixer.window, chunks, partial)

@@ -17,7 +17,7 @@ import torch
 from .library import kernels, optional_kernels
 
 F32, BF16 = 0, 1
-ACT = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2}
+ACT = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "sigmoid": 4}
 
 _STATUS = {-1: "unsupported dtype", -2: "a size that the kernel does not take",
            -3: "misaligned pointer or stride", -4: "size too large for this kernel"}
@@ -736,6 +736,162 @@ def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_
         _ptr(slot_mapping), _ptr(part), _ptr(counters), _ptr(grid_counter), _ptr(tcgen05_error_flag(x.device)), _stream(),
         _ptr(trace))
     _check(st, "decode_layers", f"layers={n_layers} rows={M} width={d} heads={n_head}/{n_kv_head} head_dim={head_dim} inner={F}")
+
+
+def linear_heads(x, w_hnk, out):
+    """Per head h: out[:, h*N:(h+1)*N] = x[:, h*K:(h+1)*K] @ w_hnk[h]^T; ``w_hnk`` is ``[heads, N, K]``, x and out
+    are 2-D with unit column stride (views of wider buffers are fine).  32-bit: this package's FFMA product,
+    head by head; bfloat16: one strided batched product of the library."""
+    _need_cuda(x, w_hnk, out)
+    H, N, K = w_hnk.shape
+    T = x.shape[0]
+    assert x.shape[1] == H * K and out.shape == (T, H * N) and x.stride(1) == 1 and out.stride(1) == 1
+    assert w_hnk.is_contiguous() and x.dtype == w_hnk.dtype == out.dtype
+    if T == 0:
+        return
+    if x.dtype == torch.float32:
+        for h in range(H):
+            linear_f32(x[:, h * K:(h + 1) * K], w_hnk[h], None, None, out[:, h * N:(h + 1) * N], w_is_nk=True)
+        return
+    xv = x.as_strided((H, T, K), (K, x.stride(0), 1), x.storage_offset())
+    ov = out.as_strided((H, T, N), (N, out.stride(0), 1), out.storage_offset())
+    torch.bmm(xv, w_hnk.transpose(1, 2), out=ov)
+
+
+def rms_norm(x, weight, eps, out, parts: int = 1, gate=None, gate_act="silu"):
+    """out = v / sqrt(mean(v^2) + eps) * weight in ``parts`` equal parts of the row, each by its own mean, with
+    v = x * act(gate) if a gate is given (the gate comes BEFORE the norm).  x: 32-bit or ``out``'s type; gate and out:
+    the compute type; views with unit column stride are fine.  Arithmetic in 32-bit."""
+    _need_cuda(x, weight, out, gate)
+    rows, n = x.shape
+    assert n % parts == 0 and out.shape == x.shape and x.stride(1) == 1 and out.stride(1) == 1
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == n and weight.is_contiguous())
+    assert gate is None or (gate.shape == x.shape and gate.stride(1) == 1 and gate.dtype == out.dtype)
+    st = kernels().cbis_rms_norm(_ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(gate),
+                                 c_int(gate.stride(0) if gate is not None else 0), c_int(ACT[gate_act]), _ptr(weight),
+                                 c_float(eps), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(rows),
+                                 c_int(parts), c_int(n // parts), _stream())
+    _check(st, "rms_norm", f"rows={rows} width={n} parts={parts}")
+
+
+def gate_mul(a, b, act, out):
+    """out = act(a) * b element by element (32-bit arithmetic, one rounding); a, b, out: ``[rows, n]`` of one type,
+    views with unit column stride are fine."""
+    _need_cuda(a, b, out)
+    rows, n = a.shape
+    assert b.shape == a.shape and out.shape == a.shape and a.dtype == b.dtype == out.dtype
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    st = kernels().cbis_gate_mul(_ptr(a), c_int(a.stride(0)), _ptr(b), c_int(b.stride(0)), _ptr(out), c_int(out.stride(0)),
+                                 c_int(ACT[act]), c_int(rows), c_int(n), c_int(dtype_code(a.dtype)), _stream())
+    _check(st, "gate_mul", f"rows={rows} n={n}")
+
+
+_limits = {}
+
+
+def conv_max_taps() -> int:
+    if "taps" not in _limits:
+        _limits["taps"] = int(kernels().cbis_conv_max_taps())
+    return _limits["taps"]
+
+
+def scan_max_state() -> int:
+    if "state" not in _limits:
+        _limits["state"] = int(kernels().cbis_scan_max_state())
+    return _limits["state"]
+
+
+def causal_conv_act(x, c0, channels, weight, bias, state, seg_slot, cu_rows, n_segments, max_seg_rows, act, out):
+    """Causal convolution per channel over each segment's rows, bias and activation: the channels are columns
+    ``c0 .. c0 + channels - 1`` of x; ``weight`` ``[channels, taps]`` (the last tap meets the current row) and
+    ``bias`` 32-bit; ``state`` ``[slots, >= (taps-1)*channels]`` 32-bit holds every request's last taps-1 inputs
+    (zeros at a sequence's start) and is NOT changed (``conv_state_update`` does that afterwards)."""
+    _need_cuda(x, weight, bias, state, seg_slot, cu_rows, out)
+    taps = weight.shape[1]
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (x.shape[0], channels) and out.dtype == x.dtype
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == channels
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= (taps - 1) * channels
+    st = kernels().cbis_causal_conv_act(_ptr(x), c_int(x.stride(0)), c_int(c0), _ptr(weight), _ptr(bias), _ptr(state),
+                                        ctypes.c_longlong(state.stride(0)), _ptr(seg_slot), _ptr(cu_rows), _ptr(out),
+                                        c_int(out.stride(0)), c_int(channels), c_int(taps), c_int(ACT[act]),
+                                        c_int(n_segments), c_int(max_seg_rows), c_int(dtype_code(x.dtype)), _stream())
+    _check(st, "causal_conv_act", f"channels={channels} taps={taps} segments={n_segments}")
+
+
+def conv_state_update(x, c0, channels, taps, state, seg_slot, cu_rows, n_segments):
+    """Every segment's request keeps its last ``taps - 1`` inputs (older ones move up when a segment is shorter)."""
+    _need_cuda(x, state, seg_slot, cu_rows)
+    st = kernels().cbis_conv_state_update(_ptr(x), c_int(x.stride(0)), c_int(c0), _ptr(state),
+                                          ctypes.c_longlong(state.stride(0)), _ptr(seg_slot), _ptr(cu_rows),
+                                          c_int(channels), c_int(taps), c_int(n_segments), c_int(dtype_code(x.dtype)),
+                                          _stream())
+    _check(st, "conv_state_update", f"channels={channels} taps={taps} segments={n_segments}")
+
+
+def ssm_scan(xbc, proj, dt_off, dt_bias, a_log, d_skip, state, seg_slot, cu_rows, n_segments, heads, head_dim, n_state,
+             groups, y):
+    """The selective state-space recurrence over each segment's rows, from and into ``state`` ``[slots, >= heads *
+    head_dim * n_state]`` (32-bit, laid out ``[head][column][state]``): per head, with dt = softplus(raw + dt_bias),
+    S <- exp(-exp(a_log) dt) S + dt B x^T and y = S^T C + d_skip x.  ``xbc`` rows: x | B | C (compute type); the raw
+    step sizes are columns ``dt_off ..`` of ``proj``; ``y`` ``[T, heads * head_dim]`` 32-bit."""
+    _need_cuda(xbc, proj, dt_bias, a_log, d_skip, state, seg_slot, cu_rows, y)
+    assert xbc.stride(1) == 1 and proj.stride(1) == 1 and y.dtype == torch.float32 and y.stride(1) == 1
+    assert xbc.dtype == proj.dtype and state.dtype == torch.float32 and state.stride(1) == 1
+    assert state.shape[1] >= heads * head_dim * n_state and xbc.shape[1] == heads * head_dim + 2 * groups * n_state
+    assert all(t.dtype == torch.float32 and t.numel() == heads for t in (dt_bias, a_log, d_skip))
+    st = kernels().cbis_ssm_scan(_ptr(xbc), c_int(xbc.stride(0)), _ptr(proj), c_int(proj.stride(0)), c_int(dt_off),
+                                 _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), ctypes.c_longlong(state.stride(0)),
+                                 _ptr(seg_slot), _ptr(cu_rows), _ptr(y), c_int(y.stride(0)), c_int(n_segments),
+                                 c_int(heads), c_int(head_dim), c_int(n_state), c_int(groups),
+                                 c_int(dtype_code(xbc.dtype)), _stream())
+    _check(st, "ssm_scan", f"heads={heads} head_dim={head_dim} state={n_state} groups={groups} segments={n_segments}")
+
+
+ROUTE_SCORE = {"sigmoid": 0, "softmax": 1}
+
+
+def route_topk(h, router, top, score, renormalize, ids, weights):
+    """Router logits ``h @ router^T`` in 32-bit, scores by ``score``, the ``top`` largest per row into ``ids``
+    (int32 ``[rows, top]``) with their weights (float32; divided by their sum with ``renormalize``)."""
+    _need_cuda(h, router, ids, weights)
+    rows, W = h.shape
+    E = router.shape[0]
+    assert h.stride(1) == 1 and router.is_contiguous() and router.shape[1] == W and router.dtype == h.dtype
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
+    assert ids.shape == (rows, top) and weights.shape == (rows, top)
+    st = kernels().cbis_route_topk(_ptr(h), c_int(h.stride(0)), _ptr(router), _ptr(ids), _ptr(weights), c_int(rows),
+                                   c_int(W), c_int(E), c_int(top), c_int(ROUTE_SCORE[score]), c_int(1 if renormalize else 0),
+                                   c_int(dtype_code(h.dtype)), _stream())
+    _check(st, "route_topk", f"rows={rows} experts={E} top={top}")
+
+
+def routed_gate_up(h, gate_up, ids, weights, act, weight_on_input, hidden):
+    """hidden[(row, choice)] = act(s * gate_e(h[row])) * (s * up_e(h[row])), e the choice's expert, s its weight if
+    the weight multiplies the expert's input, else 1.  ``gate_up`` ``[experts, 2 * inner, width]``."""
+    _need_cuda(h, gate_up, ids, weights, hidden)
+    rows, W = h.shape
+    E, F2, _ = gate_up.shape
+    top = ids.shape[1]
+    assert h.stride(1) == 1 and gate_up.is_contiguous() and gate_up.shape[2] == W and hidden.is_contiguous()
+    assert hidden.shape == (rows * top, F2 // 2) and hidden.dtype == h.dtype == gate_up.dtype
+    st = kernels().cbis_routed_gate_up(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(ids), _ptr(weights), _ptr(hidden),
+                                       c_int(rows), c_int(W), c_int(F2 // 2), c_int(top), c_int(ACT[act]),
+                                       c_int(1 if weight_on_input else 0), c_int(dtype_code(h.dtype)), _stream())
+    _check(st, "routed_gate_up", f"rows={rows} width={W} inner={F2 // 2} top={top}")
+
+
+def routed_down(hidden, down, ids, weights, weight_on_input, out):
+    """out[row] = the sum over the row's choices of down_e(hidden[(row, choice)]) (times the choice's weight unless
+    it already multiplied the input); ``down`` ``[experts, width, inner]``; out 32-bit."""
+    _need_cuda(hidden, down, ids, weights, out)
+    E, W, F = down.shape
+    rows, top = ids.shape
+    assert hidden.is_contiguous() and hidden.shape == (rows * top, F) and down.is_contiguous() and hidden.dtype == down.dtype
+    assert out.dtype == torch.float32 and out.shape == (rows, W) and out.stride(1) == 1
+    st = kernels().cbis_routed_down(_ptr(hidden), _ptr(down), _ptr(ids), _ptr(weights), _ptr(out), c_int(out.stride(0)),
+                                    c_int(rows), c_int(W), c_int(F), c_int(top), c_int(1 if weight_on_input else 0),
+                                    c_int(dtype_code(hidden.dtype)), _stream())
+    _check(st, "routed_down", f"rows={rows} width={W} inner={F} top={top}")
 
 
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):

@@ -2,10 +2,14 @@ from .base import (AttentionLike, Block, CacheArray, CacheNeed, Delta, Embedding
                    PositionEncoding, StateNeed, make_block, make_embedding, make_feed_forward, make_head, make_mixer,
                    make_norm, make_position, register_block, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position)
-from . import attention, blocks, dense, embedding, head, layernorm, positions  # noqa: F401  (register the built-in kinds)
+from . import (attention, blocks, dense, embedding, head, latent_attention, layernorm, positions,  # noqa: F401
+               routed, state_space)  # (importing them registers the built-in kinds)
 from .attention import PagedAttention
-from .blocks import PreNormBlock
-from .dense import DenseFeedForward
+from .blocks import ParallelBlock, PreNormBlock
+from .dense import DenseFeedForward, GatedFeedForward, NoFeedForward
+from .latent_attention import LatentAttention
+from .routed import RoutedFeedForward
+from .state_space import StateSpaceMixer
 from .embedding import TokenTable
 from .head import LinearHead
 from .layernorm import LayerNorm, NoNorm

@@ -141,4 +141,23 @@ class _DecodeLayersPlan:
                           counters, self.grid_counter, getattr(self, "trace", None))
 
 
+class ParallelBlock(Block):
+    """h = norm(x); x += mixer(h) + feed_forward(h): one norm, both parts read its output, and both results are
+    added together.  The second norm of the block interface is not used (a layer names "none" for it).  The mixer's
+    result is added at once; the feed-forward's is handed on as pending and added by the next norm."""
+
+    def forward(self, ctx, x, pending, cache, state):
+        h = self.norm_mixer.forward(ctx, x, pending)
+        ctx.residual = x
+        d = self.mixer.forward(ctx, h, cache, state)
+        ctx.residual = None
+        if d is not None:
+            ops.add_delta(x, d.value, d.bias)
+        ctx.residual = x
+        d = self.feed_forward.forward(ctx, h)
+        ctx.residual = None
+        return d
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("parallel", ParallelBlock)

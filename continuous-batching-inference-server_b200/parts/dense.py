@@ -53,3 +53,51 @@ class DenseFeedForward(FeedForward):
 
 
 register_feed_forward("dense", DenseFeedForward)
+
+
+class GatedFeedForward(FeedForward):
+    """down(act(gate h) * (up h)): three matrices stored ``[out, in]``, no biases; the gate's and the up
+    projection's rows form one matrix, so one product gives both, and the activation and the product of the two
+    halves are taken in 32-bit and rounded once.  ``names``: what follows the layer's prefix in the names of the gate,
+    up and down matrices."""
+
+    def __init__(self, width: int, inner: int, activation: str = "silu", names=("mlp.gate", "mlp.up", "mlp.down")):
+        if activation not in ops.ACT or not activation:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(k for k in ops.ACT if k)}")
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.gate_name, self.up_name, self.down_name = names
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self, prefix):
+        return [TensorDecl(prefix + self.gate_name, (self.inner, self.width)),
+                TensorDecl(prefix + self.up_name, (self.inner, self.width)),
+                TensorDecl(prefix + self.down_name, (self.width, self.inner))]
+
+    def load(self, prefix, tensors, dtype, device):
+        self.w_gate_up = torch.cat([self._matrix(tensors[prefix + self.gate_name], dtype, device),
+                                    self._matrix(tensors[prefix + self.up_name], dtype, device)]).contiguous()
+        self.w_down = self._matrix(tensors[prefix + self.down_name], dtype, device)
+
+    def streamed_weights(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, ctx, h):
+        F = self.inner
+        gu = ops.linear(h, self.w_gate_up, None)
+        a = torch.empty((h.shape[0], F), dtype=h.dtype, device=h.device)
+        ops.gate_mul(gu[:, :F], gu[:, F:], self.activation, a)
+        return Delta(ops.linear(a, self.w_down, None, None, out_dtype=torch.float32))
+
+
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: nothing is added."""
+
+    def __init__(self, width: int):
+        self.width = int(width)
+
+    def forward(self, ctx, h):
+        return None
+
+
+register_feed_forward("gated", GatedFeedForward)
+register_feed_forward("nothing", NoFeedForward)

@@ -14,19 +14,21 @@ class LayerNorm(Norm):
     """y = (x - mean) * rsqrt(var + eps) * weight + bias over the last dim, biased variance,
     statistics in 32-bit (reference: kernels/elementwise.cu:21-57; eps is a literal there, :51)."""
 
-    def __init__(self, width: int, eps: float):
+    def __init__(self, width: int, eps: float, names=("weight", "bias")):
+        """``names``: what follows the norm's prefix in the names of its weight and its bias."""
         self.width, self.eps = int(width), float(eps)
+        self.weight_name, self.bias_name = names
         if not 0 < self.width <= ops.NORM_MAX_WIDTH:
             raise ValueError(f"LayerNorm: width {self.width} is outside 1..{ops.NORM_MAX_WIDTH}, the widest row the kernel takes")
         self.weight = self.bias = None
 
     def tensors(self, prefix):
-        return [TensorDecl(prefix + "weight", (self.width,), "norm_weight"),
-                TensorDecl(prefix + "bias", (self.width,), "norm_bias")]
+        return [TensorDecl(prefix + self.weight_name, (self.width,), "norm_weight"),
+                TensorDecl(prefix + self.bias_name, (self.width,), "norm_bias")]
 
     def load(self, prefix, tensors, dtype, device):
-        self.weight = self._vector(tensors[prefix + "weight"], device)
-        self.bias = self._vector(tensors[prefix + "bias"], device)
+        self.weight = self._vector(tensors[prefix + self.weight_name], device)
+        self.bias = self._vector(tensors[prefix + self.bias_name], device)
 
     def as_layernorm(self):
         return (self.weight, self.bias, self.eps) if self.weight is not None and self.bias is not None else None
