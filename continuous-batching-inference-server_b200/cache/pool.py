@@ -108,8 +108,8 @@ class CachePool:
                     at += size
                 self.layer_cache[li] = LayerCache(gi, arrays, page_size, g.need.window)
             specs.append(host().GroupSpec(page_size, g.num_pages, g.need.window))
-        if not specs:  # a model without any cache still needs request slots
-            specs.append(host().GroupSpec(page_size, 0, 0))
+        if not specs:  # a model without any cache still needs request slots and lengths: pages that are counted only
+            specs.append(host().GroupSpec(page_size, int(num_pages), 0))
         for li, layer in enumerate(model.layers):
             src = layer.spec.cache_source
             if src is not None:

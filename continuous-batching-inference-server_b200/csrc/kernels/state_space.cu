@@ -133,12 +133,15 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
     float xn = 0.f, dtn = 0.f, Bn[NPL], Cn[NPL];
     if (i_row + 1 < n_rows) fetch(r + 1, xn, dtn, Bn, Cn);
     const float dt = softplus_f32(dtr + bias);
-    const float decay = expf(neg_a * dt);
+    // The decay is applied as S += (decay - 1) S with decay - 1 = expm1(-exp(A_log) dt): a decay close to 1 rounded
+    // to a float just below 1 loses most of the digits of 1 - decay, the same way at every step when the step size
+    // barely changes, and a state that is read a thousand tokens later would carry a thousand times that error.
+    const float decay_m1 = expm1f(neg_a * dt);
     const float dx = dt * xv;
     float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
-      S[i] = fmaf(decay, S[i], Bv[i] * dx);
+      S[i] = fmaf(decay_m1, S[i], fmaf(Bv[i], dx, S[i]));
       acc = fmaf(S[i], Cv[i], acc);
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);

@@ -30,11 +30,16 @@ def gated_feed_forward(h, gate, up, down):
     return (silu(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def routed_experts(h, router, experts, top):
+def routed_experts(h, router, experts, top, gaps=None):
     """experts: list of (gate, up, down).  Scores are sigmoids of the router's logits; the ``top`` largest
-    are taken as they are; each chosen expert is fed its score times h."""
-    s = torch.sigmoid(h @ router.T)
+    are taken as they are; each chosen expert is fed its score times h.  ``gaps`` (a list) takes, per row, how far
+    the last chosen logit lies above the first one not chosen (a small gap is a close call that rounding may turn)."""
+    z = h @ router.T
+    s = torch.sigmoid(z)
     out = torch.zeros(h.shape[0], experts[0][2].shape[0], dtype=h.dtype)
+    if gaps is not None:
+        ranked = torch.sort(z, dim=1, descending=True).values
+        gaps.append(ranked[:, top - 1] - ranked[:, top] if top < z.shape[1] else torch.full((h.shape[0],), float("inf")))
     for t in range(h.shape[0]):
         order = sorted(range(s.shape[1]), key=lambda e: (-s[t, e].item(), e))[:top]
         for e in order:
@@ -104,8 +109,9 @@ def sub(w, prefix):
     return {k[len(prefix):]: v for k, v in w.items() if k.startswith(prefix)}
 
 
-def forward(config, w, tokens, residuals=None):
-    """Logits [T, vocab] of one whole sequence; ``residuals`` (a list) takes the stream after every layer."""
+def forward(config, w, tokens, residuals=None, gaps=None):
+    """Logits [T, vocab] of one whole sequence; ``residuals`` (a list) takes the stream after every layer,
+    ``gaps`` (a list) every routed layer's gaps between chosen and not chosen experts."""
     w = {k: v.double() for k, v in w.items()}
     eps = config["norm"]["eps"]
     x = w["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
@@ -133,7 +139,7 @@ def forward(config, w, tokens, residuals=None):
             elif ff["kind"] == "moe":
                 n = ff["router"]["experts"]
                 experts = [(q[f"e{e}.gate"], q[f"e{e}.up"], q[f"e{e}.down"]) for e in range(n)]
-                fed = routed_experts(h, q["router"], experts, ff["router"]["top"])
+                fed = routed_experts(h, q["router"], experts, ff["router"]["top"], gaps)
             else:
                 raise ValueError(ff["kind"])
         x = x + (mixed + fed)
