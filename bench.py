@@ -115,10 +115,12 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching"],
+    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra"],
                     help="1.3b: the default measurement; 6.7b: batch-64 decode at context 2,048; "
                          "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each); "
-                         "batching: the reference's own workload at the reference's own sizes (both --impl arms)")
+                         "batching: the reference's own workload at the reference's own sizes (both --impl arms); "
+                         "vekedra: prefill and decode of the Vekedra design at two layer sizes beside the GPT-2 style model "
+                         "of equal width and depth, and its own kernels one by one against their bytes")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
@@ -151,6 +153,8 @@ def main() -> int:
     torch.cuda.set_device(0)
     if args.config == "xl":
         return mixed_workload(args, cb, torch)
+    if args.config == "vekedra":
+        return vekedra_workload(args, cb, torch)
     if args.config == "6.7b":
         args.skip_points = True
         args.batch = args.batch or 64
@@ -415,6 +419,193 @@ def mixed_workload(args, cb, torch) -> int:
                    "n_embd": 1600, "n_head": 25, "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024,
                    "requests": n_req, "max_batched_tokens": 2048, "prefill_chunk": 512, "page_size": args.page_size}}))
     return 0
+
+
+def vekedra_sizes(width, layers):
+    """A Vekedra configuration with layers of the sizes a model of this width would have: of every four layers one
+    latent attention that keeps its latents, two state-space layers and one latent attention that reads the first
+    one's; dense and routed feed-forwards in turn."""
+    big = width >= 2048
+    lat = {"dim": 128 if big else 64, "heads": 16, "kv_rank": 128, "mask": {"size": 1024 if big else 512},
+           "scale": (128 if big else 64) ** -0.5, "vdim": 128 if big else 64}
+    ssm = {"conv": 4, "groups": 8 if big else 1, "heads": 2 * width // 64, "norm_groups": 1, "state": 128 if big else 64,
+           "vdim": 64}
+    dense = {"kind": "dense", "ff": 11 * width // 4}
+    moe = {"kind": "moe", "expert": {"ff": 11 * width // 16}, "router": {"experts": 16 if big else 8, "top": 2}}
+    out = []
+    for i in range(layers):
+        kind = ("latent_attention", "mamba2", "mamba2", "latent_attention")[i % 4]
+        mixer = dict(ssm if kind == "mamba2" else lat)
+        if i % 4 == 3:
+            mixer["kv_from"] = i - 3
+        out.append({"type": kind, "mixer": mixer, "mlp": dict(dense if i % 2 == 0 else moe)})
+    return {"architecture": "Vekedra", "embedding": {"scale": 1.0}, "layers": out, "norm": {"eps": 1e-5},
+            "vocab": 32000, "width": width}
+
+
+def vekedra_workload(args, cb, torch) -> int:
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 from context 1,024, the captured step with
+    argmax on the device) of the Vekedra design at two layer sizes, each beside the GPT-2 style model of equal width
+    and depth; then the design's own kernels alone, at the larger size, against the bytes they have to move."""
+    from cbis_b200.engine import StepEntry
+    from cbis_b200.kernels import ops
+    pk = peaks()
+    P, T, B = 2048, 2048, args.batch or 8
+    steps, warm = min(args.steps, 128), max(3, min(args.warmup, 8))
+    layers = args.layers or 8
+    gen = torch.Generator().manual_seed(0)
+
+    def measure(cfgd, vocab):
+        eng = cb.Engine.from_random(cfgd, seed=1234, dtype="bfloat16", page_size=args.page_size, max_tokens=B * P,
+                                    max_num_seqs=B, max_batched_tokens=T, prefill_chunk=T, max_model_len=P)
+        mgr = eng.pool.manager
+        toks = torch.randint(0, vocab, (B, T), generator=gen).tolist()
+        times = []
+        for it in range(3 + 5):
+            slot = eng.open_request(it)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.forward_step([StepEntry(slot, 0, toks[0], [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+            eng.close_request(slot)
+        prefill_ms = statistics.median(times)
+        slots = [eng.open_request(100 + i) for i in range(B)]
+        for i, s in enumerate(slots):
+            eng.forward_step([StepEntry(s, 0, toks[i][:1024], [])])
+            assert mgr.append(s, warm + steps + 2)
+        ops.reset_launch_count()
+        loop = eng.runner.decode_loop([StepEntry(s, 1024, [1], [0]) for s in slots])
+        launches = ops.launch_count() // 2
+        loop.run(warm)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        loop.run(steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        weights = eng.model.weight_bytes()
+        del loop
+        for s in slots:
+            eng.close_request(s)
+        del eng
+        torch.cuda.empty_cache()
+        return {"prefill_tokens_per_s": round(T / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tokens_per_s": round(B / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
+                "decode_launches_per_step": launches, "weight_bytes": int(weights),
+                "decode_weight_stream_frac": round(weights / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for width in (1024, 2048):
+        vek = vekedra_sizes(width, layers)
+        gpt = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=layers, n_embd=width, n_head=16,
+                   n_inner=4 * width, vocab_size=32000, n_positions=P, activation_function="gelu",
+                   layer_norm_epsilon=1e-5, tie_word_embeddings=False)
+        sizes[f"width_{width}"] = {"vekedra": measure(vek, 32000), "gpt2_style": measure(gpt, 32000)}
+    clocks = sampler.stop()
+    line = {"metric": f"Vekedra prefill and decode tokens/s beside the GPT-2 style model of equal width and depth "
+                      f"({layers} layers, batch {B}, prompt {T})", "unit": "tokens/s", "n_gpus": 1, "impl": "b200",
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "higher_is_better": True,
+            "value": sizes["width_2048"]["vekedra"]["decode_tokens_per_s"], "sizes": sizes,
+            "kernels": vekedra_kernels(torch, ops, pk), "clocks": clocks, "peaks": pk}
+    print(json.dumps(line))
+    return 0
+
+
+def vekedra_kernels(torch, ops, pk):
+    """Microseconds of the design's own kernels alone (each replayed from a CUDA graph over buffers that rotate, so that
+    inputs come from memory) at the layer sizes of width 2,048, with the bytes each has to move over its time as a
+    fraction of the measured copy bandwidth; and the closest model's like kernel (LayerNorm over the same rows)."""
+    W, H, Pd, N, G, K = 2048, 64, 64, 128, 8, 4
+    inner, C = H * Pd, H * Pd + 2 * G * N
+    d_proj = 2 * inner + 2 * G * N + H
+    bf = torch.bfloat16
+    out = {}
+
+    def timed(make, nbytes, name, reps=20, copies=4):
+        fns = [make() for _ in range(copies)]
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / reps / copies * 1e3
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "frac_of_copy_bandwidth": round(nbytes / us / 1e3 / pk["hbm_gbs"], 4)}
+
+    for rows, segs, tag in ((2048, 1, "prefill_2048"), (8, 8, "decode_8")):
+        per = rows // segs
+        seg_slot = torch.arange(segs, dtype=torch.int32, device="cuda")
+        cu = torch.arange(0, rows + 1, per, dtype=torch.int32, device="cuda")
+
+        def conv():
+            proj = torch.randn(rows, d_proj, device="cuda").to(bf)
+            w, b = torch.randn(C, K, device="cuda"), torch.randn(C, device="cuda")
+            st = torch.zeros(segs, (K - 1) * C, device="cuda")
+            o = torch.empty(rows, C, dtype=bf, device="cuda")
+            return lambda: ops.causal_conv_act(proj, inner, C, w, b, st, seg_slot, cu, segs, per, "silu", o)
+        timed(conv, rows * C * 4 + segs * (K - 1) * C * 4, f"causal_conv_act_{tag}")
+
+        def scan():
+            xbc = (torch.randn(rows, C, device="cuda") * 0.5).to(bf)
+            proj = torch.randn(rows, d_proj, device="cuda").to(bf)
+            v = [torch.zeros(H, device="cuda") for _ in range(3)]
+            st = torch.zeros(segs, inner * N, device="cuda")
+            y = torch.empty(rows, inner, device="cuda")
+            return lambda: ops.ssm_scan(xbc, proj, d_proj - H, v[0], v[1], v[2], st, seg_slot, cu, segs, H, Pd, N, G, y)
+        timed(scan, rows * (C * 2 + inner * 4) + 2 * segs * inner * N * 4, f"ssm_scan_{tag}")
+
+        def gnorm():
+            y = torch.randn(rows, inner, device="cuda")
+            z = torch.randn(rows, d_proj, device="cuda").to(bf)
+            w = torch.ones(inner, device="cuda")
+            o = torch.empty(rows, inner, dtype=bf, device="cuda")
+            return lambda: ops.rms_norm(y, w, 1e-5, o, parts=1, gate=z[:, :inner])
+        timed(gnorm, rows * inner * (4 + 2 + 2), f"gated_rms_norm_{tag}")
+
+        def lnorm():
+            x = torch.randn(rows, inner, device="cuda")
+            d = torch.randn(rows, inner, device="cuda")
+            w, b = torch.ones(inner, device="cuda"), torch.zeros(inner, device="cuda")
+            o = torch.empty(rows, inner, dtype=bf, device="cuda")
+            return lambda: ops.add_layernorm(x, d, None, w, b, 1e-5, o)
+        timed(lnorm, rows * inner * (4 + 4 + 4 + 2), f"closest_model_add_layernorm_{tag}")
+
+        E, F, top = 16, 1408, 2
+
+        def experts():
+            h = torch.randn(rows, W, device="cuda").to(bf)
+            router = torch.randn(E, W, device="cuda").to(bf)
+            gu = (torch.randn(E, 2 * F, W, device="cuda") * 0.02).to(bf)
+            dn = (torch.randn(E, W, F, device="cuda") * 0.02).to(bf)
+            ids = torch.empty(rows, top, dtype=torch.int32, device="cuda")
+            wt = torch.empty(rows, top, device="cuda")
+            hid = torch.empty(rows * top, F, dtype=bf, device="cuda")
+            o = torch.empty(rows, W, device="cuda")
+
+            def run():
+                ops.route_topk(h, router, top, "sigmoid", False, ids, wt)
+                ops.routed_gate_up(h, gu, ids, wt, "silu", True, hid)
+                ops.routed_down(hid, dn, ids, wt, True, o)
+            return run
+        touched = min(E, rows * top)
+        timed(experts, touched * 3 * F * W * 2 + rows * W * 6, f"routed_feed_forward_{tag}", copies=2)
+    return out
 
 
 def all_decoding(eng, batch):

@@ -87,10 +87,24 @@ routed_gate_up_kernel(const TT* h, int h_ld, const TT* __restrict__ gate_up, con
   const TT* wg = gate_up + ((size_t)e * 2 * F + f) * W;
   const TT* wu = wg + (size_t)F * W;
   float g = 0.f, u = 0.f;
-  for (int k = lane; k < W; k += 32) {
-    const float x = hs[k];
-    g = fmaf(to_f32(wg[k]), x, g);
-    u = fmaf(to_f32(wu[k]), x, u);
+  constexpr int V = 16 / (int)sizeof(TT);      // elements of a 16-byte load
+  if (W % V == 0 && !(((uintptr_t)wg | (uintptr_t)wu) & 15)) {
+    for (int k = lane * V; k < W; k += 32 * V) {
+      TT a[V], b[V];
+      *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(wg + k);
+      *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(wu + k);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        g = fmaf(to_f32(a[i]), hs[k + i], g);
+        u = fmaf(to_f32(b[i]), hs[k + i], u);
+      }
+    }
+  } else {
+    for (int k = lane; k < W; k += 32) {
+      const float x = hs[k];
+      g = fmaf(to_f32(wg[k]), x, g);
+      u = fmaf(to_f32(wu[k]), x, u);
+    }
   }
   g = warp_sum(g);
   u = warp_sum(u);
@@ -101,11 +115,12 @@ routed_gate_up_kernel(const TT* h, int h_ld, const TT* __restrict__ gate_up, con
 }
 
 // grid (rows, ceil(W / 8)), 256 threads: out[row, n] = sum over the row's choices k of
-//   (weight on output ? weight : 1) * (Wd_e[n, :] . hid[row * top + k, :]),   down: [E, W, F].  out is 32-bit.
+//   (weight on output ? weight : 1) * (Wd_e[n, :] . hid[row * top + k, :]),   down: [E, W, F].  out is 32-bit and is
+// overwritten, or added to with `accumulate`.
 template <typename TT>
 __global__ void __launch_bounds__(256)
 routed_down_kernel(const TT* hid, const TT* __restrict__ down, const int* ids, const float* weights, float* out,
-                   int out_ld, int W, int F, int top, int weight_on_input) {
+                   int out_ld, int W, int F, int top, int weight_on_input, int accumulate) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, n = blockIdx.y * 8 + (threadIdx.x >> 5);
@@ -116,16 +131,240 @@ routed_down_kernel(const TT* hid, const TT* __restrict__ down, const int* ids, c
     const TT* wd = down + ((size_t)ids[pair] * W + n) * F;
     const TT* hp = hid + (size_t)pair * F;
     float acc = 0.f;
-    for (int f = lane; f < F; f += 32) acc = fmaf(to_f32(wd[f]), to_f32(hp[f]), acc);
+    constexpr int V = 16 / (int)sizeof(TT);
+    if (F % V == 0 && !(((uintptr_t)wd | (uintptr_t)hp) & 15)) {
+      for (int f = lane * V; f < F; f += 32 * V) {
+        TT a[V], b[V];
+        *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(wd + f);
+        *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(hp + f);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc = fmaf(to_f32(a[i]), to_f32(b[i]), acc);
+      }
+    } else {
+      for (int f = lane; f < F; f += 32) acc = fmaf(to_f32(wd[f]), to_f32(hp[f]), acc);
+    }
     acc = warp_sum(acc);
     total += weight_on_input ? acc : acc * weights[pair];
   }
-  if (lane == 0) out[(size_t)row * out_ld + n] = total;
+  if (lane == 0) {
+    float* o = out + (size_t)row * out_ld + n;
+    *o = accumulate ? *o + total : total;
+  }
+}
+
+// ---- many rows (bfloat16): the (row, choice) pairs sorted by expert, an expert's pairs in tiles of 64 rows, each tile's
+// products on the tensor cores (mma.sync m16n8k16, 32-bit sums).  A pair's result depends on its own row alone: its
+// place in a tile changes no sum's order.
+constexpr int kTileM = 64, kTileN = 64, kTileK = 32, kLd = kTileK + 8;   // shared rows padded to 80 bytes
+
+// One block.  offsets [E + 1]; sorted [pairs]: the pairs expert by expert; per tile its expert, its first place in
+// `sorted` and its rows; n_tiles [1].
+__global__ void __launch_bounds__(1024)
+routed_plan_kernel(const int* ids, int n_pairs, int E, int* offsets, int* sorted, int* tile_expert, int* tile_start,
+                   int* tile_rows, int* n_tiles) {
+  extern __shared__ int plan_smem[];
+  int* count = plan_smem;          // E
+  int* cursor = plan_smem + E;     // E
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, t = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      for (int r = 0; r < count[e]; r += kTileM) {
+        tile_expert[t] = e;
+        tile_start[t] = at + r;
+        tile_rows[t] = min(kTileM, count[e] - r);
+        ++t;
+      }
+      at += count[e];
+    }
+    offsets[E] = at;
+    *n_tiles = t;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < E) sorted[offsets[e] + atomicAdd(&cursor[e], 1)] = p;
+  }
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// grid (max tiles, ceil(N / 64)), 128 threads: warp w owns rows 16 w .. 16 w + 15 of the tile and all 64 columns.
+// DUAL: A = h[pair / top] (K = width), B = the expert's gate rows and up rows; out = hid[pair] = act(s g) * (s u).
+// else: A = hid[pair] (K = inner), B = the expert's down matrix; y[pair] (or y[row] when top is 1) = sum (* weight).
+template <bool DUAL>
+__global__ void __launch_bounds__(128)
+routed_tiles_kernel(const __nv_bfloat16* A, int a_ld, const __nv_bfloat16* __restrict__ Bw, const int* sorted,
+                    const float* weights, const int* tile_expert, const int* tile_start, const int* tile_rows,
+                    const int* n_tiles, void* out, int out_ld, int N, int K, int top, int act, int weight_on_input) {
+  __shared__ __align__(16) __nv_bfloat16 As[kTileM][kLd];
+  __shared__ __align__(16) __nv_bfloat16 Bs[DUAL ? 2 : 1][kTileN][kLd];
+  __shared__ int pair_of[kTileM];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.x;
+  if (tile >= *n_tiles) return;
+  const int e = tile_expert[tile], start = tile_start[tile], rows = tile_rows[tile];
+  const int n0 = blockIdx.y * kTileN;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < kTileM) pair_of[threadIdx.x] = threadIdx.x < rows ? sorted[start + threadIdx.x] : -1;
+  __syncthreads();
+  const __nv_bfloat16* B0 = Bw + (size_t)e * (DUAL ? 2 : 1) * N * K;      // [N (x2), K]
+  float acc[DUAL ? 2 : 1][8][4];
+#pragma unroll
+  for (int m = 0; m < (DUAL ? 2 : 1); ++m)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+    // 64 rows x 32 columns = 256 pieces of 16 bytes per matrix, two per thread
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = threadIdx.x + it * 128, r = idx >> 2, kc = (idx & 3) * 8;
+      const bool k_ok = k0 + kc < K;
+      const int pair = pair_of[r];
+      uint4 v = zero;
+      if (pair >= 0 && k_ok) v = *reinterpret_cast<const uint4*>(A + (size_t)(DUAL ? pair / top : pair) * a_ld + k0 + kc);
+      *reinterpret_cast<uint4*>(&As[r][kc]) = v;
+      const bool n_ok = n0 + r < N && k_ok;
+      v = zero;
+      if (n_ok) v = *reinterpret_cast<const uint4*>(B0 + (size_t)(n0 + r) * K + k0 + kc);
+      *reinterpret_cast<uint4*>(&Bs[0][r][kc]) = v;
+      if (DUAL) {
+        v = zero;
+        if (n_ok) v = *reinterpret_cast<const uint4*>(B0 + (size_t)(N + n0 + r) * K + k0 + kc);
+        *reinterpret_cast<uint4*>(&Bs[DUAL ? 1 : 0][r][kc]) = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kTileK; kk += 16) {
+      uint32_t a[4];
+      const int ar = warp * 16 + (lane >> 2), ak = kk + (lane & 3) * 2;
+      a[0] = *reinterpret_cast<const uint32_t*>(&As[ar][ak]);
+      a[1] = *reinterpret_cast<const uint32_t*>(&As[ar + 8][ak]);
+      a[2] = *reinterpret_cast<const uint32_t*>(&As[ar][ak + 8]);
+      a[3] = *reinterpret_cast<const uint32_t*>(&As[ar + 8][ak + 8]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int bn = j * 8 + (lane >> 2);
+#pragma unroll
+        for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
+          uint32_t b[2];
+          b[0] = *reinterpret_cast<const uint32_t*>(&Bs[m][bn][ak]);
+          b[1] = *reinterpret_cast<const uint32_t*>(&Bs[m][bn][ak + 8]);
+          mma_bf16(acc[m][j], a, b);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = warp * 16 + (lane >> 2) + half * 8;
+    const int pair = pair_of[r];
+    if (pair < 0) continue;
+    const float w = weights[pair];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int n = n0 + j * 8 + (lane & 3) * 2 + i;
+        if (n >= N) continue;
+        if (DUAL) {
+          const float s = weight_on_input ? w : 1.f;
+          from_f32(static_cast<__nv_bfloat16*>(out)[(size_t)pair * out_ld + n],
+                   activate(s * acc[0][j][half * 2 + i], act) * (s * acc[DUAL ? 1 : 0][j][half * 2 + i]));
+        } else {
+          static_cast<float*>(out)[(size_t)pair * out_ld + n] = weight_on_input ? acc[0][j][half * 2 + i] : w * acc[0][j][half * 2 + i];
+        }
+      }
+  }
+}
+
+// out[row, n] (+)= y[row * top + 0, n] + y[row * top + 1, n] + ..., in that order; 32-bit.
+__global__ void routed_combine_kernel(const float* y, float* out, int out_ld, int rows, int W, int top, int accumulate) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)rows * W;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / W;
+    const int n = (int)(i % W);
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += y[(r * top + k) * W + n];
+    float* o = out + r * out_ld + n;
+    *o = accumulate ? *o + v : v;
+  }
 }
 
 }  // namespace cbis
 
 using namespace cbis;
+
+CBIS_EXPORT int cbis_routed_tile_rows() { return kTileM; }
+
+// ints of scratch the plan needs: offsets (E + 1), sorted (pairs), three tables of max_tiles, n_tiles (1)
+CBIS_EXPORT long long cbis_routed_plan_ints(int pairs, int E) {
+  const long long max_tiles = (pairs + kTileM - 1) / kTileM + E;
+  return (long long)E + 1 + pairs + 3 * max_tiles + 1;
+}
+
+// The whole routed feed-forward for many rows of bfloat16: plan, gate/up tiles, down tiles, and (top > 1) the sum of a
+// row's choices.  plan: cbis_routed_plan_ints ints; hid [pairs, F] bfloat16; y [pairs, W] 32-bit (unused when top is 1);
+// out [rows, W] 32-bit, overwritten, or added to with `accumulate`.
+CBIS_EXPORT int cbis_routed_tiles(const void* h, int h_ld, const void* gate_up, const void* down, const int* ids,
+                                  const float* weights, int* plan, void* hid, float* y, float* out, int out_ld, int rows,
+                                  int W, int F, int E, int top, int act, int weight_on_input, int accumulate,
+                                  void* stream) {
+  if (rows <= 0) return CBIS_OK;
+  if (W <= 0 || F <= 0 || E <= 0 || top <= 0) return CBIS_ERR_BAD_SIZE;
+  if (W % 8 || F % 8 || h_ld % 8) return CBIS_ERR_ALIGNMENT;
+  if (((uintptr_t)h | (uintptr_t)gate_up | (uintptr_t)down | (uintptr_t)hid) & 15) return CBIS_ERR_ALIGNMENT;
+  if (E > 4096) return CBIS_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int pairs = rows * top;
+  const int max_tiles = (pairs + kTileM - 1) / kTileM + E;
+  int* offsets = plan;
+  int* sorted = offsets + E + 1;
+  int* tile_expert = sorted + pairs;
+  int* tile_start = tile_expert + max_tiles;
+  int* tile_rows = tile_start + max_tiles;
+  int* n_tiles = tile_rows + max_tiles;
+  cudaError_t err = launch_pdl(routed_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), st, ids, pairs, E,
+                               offsets, sorted, tile_expert, tile_start, tile_rows, n_tiles);
+  if (err != cudaSuccess) return (int)err;
+  typedef const __nv_bfloat16* bp;
+  err = launch_pdl(routed_tiles_kernel<true>, dim3(max_tiles, (F + kTileN - 1) / kTileN), dim3(128), 0, st, (bp)h, h_ld,
+                   (bp)gate_up, (const int*)sorted, weights, (const int*)tile_expert, (const int*)tile_start,
+                   (const int*)tile_rows, (const int*)n_tiles, hid, F, F, W, top, act, weight_on_input);
+  if (err != cudaSuccess) return (int)err;
+  const bool direct = top == 1 && !accumulate;
+  err = launch_pdl(routed_tiles_kernel<false>, dim3(max_tiles, (W + kTileN - 1) / kTileN), dim3(128), 0, st, (bp)hid, F,
+                   (bp)down, (const int*)sorted, weights, (const int*)tile_expert, (const int*)tile_start,
+                   (const int*)tile_rows, (const int*)n_tiles, (void*)(direct ? out : y), direct ? out_ld : W, W, F, top,
+                   act, weight_on_input);
+  if (err != cudaSuccess || direct) return (int)err;
+  const size_t total = (size_t)rows * W;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return (int)launch_pdl(routed_combine_kernel, dim3((int)blocks), dim3(256), 0, st, (const float*)y, out, out_ld, rows, W,
+                         top, accumulate);
+}
 
 CBIS_EXPORT int cbis_route_topk(const void* h, int h_ld, const void* router, int* ids, float* weights, int rows, int W,
                                 int E, int top, int score, int renormalize, int dtype, void* stream) {
@@ -163,8 +402,8 @@ CBIS_EXPORT int cbis_routed_gate_up(const void* h, int h_ld, const void* gate_up
 }
 
 CBIS_EXPORT int cbis_routed_down(const void* hid, const void* down, const int* ids, const float* weights, float* out,
-                                 int out_ld, int rows, int W, int F, int top, int weight_on_input, int dtype,
-                                 void* stream) {
+                                 int out_ld, int rows, int W, int F, int top, int weight_on_input, int accumulate,
+                                 int dtype, void* stream) {
   if (rows <= 0) return CBIS_OK;
   if (W <= 0 || F <= 0 || top <= 0) return CBIS_ERR_BAD_SIZE;
   if (W > 8 * 65535) return CBIS_ERR_TOO_LARGE;
@@ -172,9 +411,9 @@ CBIS_EXPORT int cbis_routed_down(const void* hid, const void* down, const int* i
   const dim3 grid(rows, (W + 7) / 8);
   if (dtype == CBIS_F32)
     return (int)launch_pdl(routed_down_kernel<float>, grid, dim3(256), 0, st, (const float*)hid, (const float*)down, ids,
-                           weights, out, out_ld, W, F, top, weight_on_input);
+                           weights, out, out_ld, W, F, top, weight_on_input, accumulate);
   if (dtype == CBIS_BF16)
     return (int)launch_pdl(routed_down_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, (const __nv_bfloat16*)hid,
-                           (const __nv_bfloat16*)down, ids, weights, out, out_ld, W, F, top, weight_on_input);
+                           (const __nv_bfloat16*)down, ids, weights, out, out_ld, W, F, top, weight_on_input, accumulate);
   return CBIS_ERR_BAD_DTYPE;
 }

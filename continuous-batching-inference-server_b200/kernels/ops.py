@@ -880,9 +880,9 @@ def routed_gate_up(h, gate_up, ids, weights, act, weight_on_input, hidden):
     _check(st, "routed_gate_up", f"rows={rows} width={W} inner={F2 // 2} top={top}")
 
 
-def routed_down(hidden, down, ids, weights, weight_on_input, out):
+def routed_down(hidden, down, ids, weights, weight_on_input, out, accumulate=False):
     """out[row] = the sum over the row's choices of down_e(hidden[(row, choice)]) (times the choice's weight unless
-    it already multiplied the input); ``down`` ``[experts, width, inner]``; out 32-bit."""
+    it already multiplied the input); ``down`` ``[experts, width, inner]``; out 32-bit, added to with ``accumulate``."""
     _need_cuda(hidden, down, ids, weights, out)
     E, W, F = down.shape
     rows, top = ids.shape
@@ -890,8 +890,62 @@ def routed_down(hidden, down, ids, weights, weight_on_input, out):
     assert out.dtype == torch.float32 and out.shape == (rows, W) and out.stride(1) == 1
     st = kernels().cbis_routed_down(_ptr(hidden), _ptr(down), _ptr(ids), _ptr(weights), _ptr(out), c_int(out.stride(0)),
                                     c_int(rows), c_int(W), c_int(F), c_int(top), c_int(1 if weight_on_input else 0),
-                                    c_int(dtype_code(hidden.dtype)), _stream())
+                                    c_int(1 if accumulate else 0), c_int(dtype_code(hidden.dtype)), _stream())
     _check(st, "routed_down", f"rows={rows} width={W} inner={F} top={top}")
+
+
+ROUTED_TILES_FROM = 33     # rows from which the routed feed-forward sorts its rows by expert and runs tiles on the tensor cores
+
+
+def routed_tiles_takes(h, gate_up, down) -> bool:
+    """Whether ``routed_tiles`` takes these rows: bfloat16, enough of them, sizes in steps of 8, aligned."""
+    W, F = gate_up.shape[2], down.shape[2]
+    return (h.dtype == torch.bfloat16 and h.shape[0] >= ROUTED_TILES_FROM and W % 8 == 0 and F % 8 == 0
+            and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0 and gate_up.shape[0] <= 4096)
+
+
+def _routed_plan_ints(pairs: int, experts: int) -> int:
+    fn = kernels().cbis_routed_plan_ints
+    fn.restype = ctypes.c_longlong
+    return int(fn(c_int(pairs), c_int(experts)))
+
+
+def routed_tiles(h, gate_up, down, ids, weights, act, weight_on_input, out, accumulate=False):
+    """The routed feed-forward for many rows of bfloat16: the (row, choice) pairs are sorted by expert on the device, an
+    expert's pairs run in tiles of 64 rows on the tensor cores (gate and up with the gated activation in one kernel,
+    then down), and a row's choices are summed in their order.  ``out`` 32-bit ``[rows, width]``, overwritten or, with
+    ``accumulate``, added to.  Nothing is read back to the host: it can be captured."""
+    _need_cuda(h, gate_up, down, ids, weights, out)
+    rows, W = h.shape
+    E, F2, _ = gate_up.shape
+    F, top = F2 // 2, ids.shape[1]
+    assert gate_up.is_contiguous() and down.is_contiguous() and down.shape == (E, W, F) and h.stride(1) == 1
+    assert out.dtype == torch.float32 and out.shape == (rows, W) and out.stride(1) == 1
+    plan = torch.empty(int(_routed_plan_ints(rows * top, E)), dtype=torch.int32, device=h.device)
+    hidden = torch.empty((rows * top, F), dtype=torch.bfloat16, device=h.device)
+    y = torch.empty((rows * top, W), dtype=torch.float32, device=h.device) if (top > 1 or accumulate) else None
+    st = kernels().cbis_routed_tiles(_ptr(h), c_int(h.stride(0)), _ptr(gate_up), _ptr(down), _ptr(ids), _ptr(weights),
+                                     _ptr(plan), _ptr(hidden), _ptr(y), _ptr(out), c_int(out.stride(0)), c_int(rows),
+                                     c_int(W), c_int(F), c_int(E), c_int(top), c_int(ACT[act]),
+                                     c_int(1 if weight_on_input else 0), c_int(1 if accumulate else 0), _stream())
+    _check(st, "routed_tiles", f"rows={rows} width={W} inner={F} experts={E} top={top}", launches=4 if y is not None else 3)
+
+
+def linear_residual(x, w_nk, residual) -> bool:
+    """residual += x @ w_nk^T by a product that adds in place, where one takes these rows (bfloat16: the TMA + tcgen05
+    product with its reduction into the 32-bit rows for prompts, the weight-streaming product for a few rows); returns
+    whether it did.  After a no the caller computes the product and hands it on to be added."""
+    if residual is None or x.dtype != torch.bfloat16 or not x.is_cuda:
+        return False
+    if linear_add_takes(x, w_nk, residual):
+        linear_add(x, w_nk, None, residual)
+        return True
+    M, K = x.shape
+    if (0 < M <= SMALL_M and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.stride(1) == 1
+            and residual.dtype == torch.float32 and residual.stride(1) == 1 and residual.shape == (M, w_nk.shape[0])):
+        gemm_small_m(x, w_nk, None, None, residual, accumulate=True)
+        return True
+    return False
 
 
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):

@@ -86,6 +86,8 @@ class GatedFeedForward(FeedForward):
         gu = ops.linear(h, self.w_gate_up, None)
         a = torch.empty((h.shape[0], F), dtype=h.dtype, device=h.device)
         ops.gate_mul(gu[:, :F], gu[:, F:], self.activation, a)
+        if ops.linear_residual(a, self.w_down, ctx.residual):       # the product adds into the residual stream itself
+            return None
         return Delta(ops.linear(a, self.w_down, None, None, out_dtype=torch.float32))
 
 

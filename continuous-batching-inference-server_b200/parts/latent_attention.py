@@ -77,6 +77,8 @@ class LatentAttention(Mixer):
         out = torch.empty((T, HV), dtype=h.dtype, device=h.device)
         ops.linear_heads(mixed, self.w_uv, out)
         ops.gate_mul(proj[:, HD:HD + HV], out, "sigmoid", out)
+        if ops.linear_residual(out, self.w_out, ctx.residual):      # the product adds into the residual stream itself
+            return None
         return Delta(ops.linear(out, self.w_out, None, None, out_dtype=torch.float32))
 
 

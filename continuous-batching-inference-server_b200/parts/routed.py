@@ -58,11 +58,19 @@ class RoutedFeedForward(FeedForward):
         ids = torch.empty((T, self.top), dtype=torch.int32, device=h.device)
         weights = torch.empty((T, self.top), dtype=torch.float32, device=h.device)
         ops.route_topk(h, self.w_router, self.top, self.score, self.renormalize, ids, weights)
-        hidden = torch.empty((T * self.top, self.inner), dtype=h.dtype, device=h.device)
-        ops.routed_gate_up(h, self.w_gate_up, ids, weights, self.activation, self.weight_on_input, hidden)
-        out = torch.empty((T, self.width), dtype=torch.float32, device=h.device)
-        ops.routed_down(hidden, self.w_down, ids, weights, self.weight_on_input, out)
-        return Delta(out)
+        # the result goes straight into the 32-bit residual rows where a block offers them
+        into = ctx.residual if ctx.residual is not None and ctx.residual.shape == (T, self.width) else None
+        out = into if into is not None else torch.empty((T, self.width), dtype=torch.float32, device=h.device)
+        if ops.routed_tiles_takes(h, self.w_gate_up, self.w_down):
+            # many rows: sorted by expert, tiles on the tensor cores
+            ops.routed_tiles(h, self.w_gate_up, self.w_down, ids, weights, self.activation, self.weight_on_input, out,
+                             accumulate=into is not None)
+        else:
+            # a few rows (decoding), and the 32-bit path: every (row, choice) streams its expert's matrices
+            hidden = torch.empty((T * self.top, self.inner), dtype=h.dtype, device=h.device)
+            ops.routed_gate_up(h, self.w_gate_up, ids, weights, self.activation, self.weight_on_input, hidden)
+            ops.routed_down(hidden, self.w_down, ids, weights, self.weight_on_input, out, accumulate=into is not None)
+        return None if into is not None else Delta(out)
 
 
 register_feed_forward("routed", RoutedFeedForward)

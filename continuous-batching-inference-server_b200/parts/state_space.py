@@ -75,6 +75,8 @@ class StateSpaceMixer(Mixer):
                      ctx.cu_rows, ctx.n_segments, self.heads, self.head_dim, self.n_state, self.groups, y)
         g = torch.empty((T, inner), dtype=h.dtype, device=h.device)
         ops.rms_norm(y, self.norm_w, self.eps, g, parts=self.norm_groups, gate=proj[:, :inner], gate_act="silu")
+        if ops.linear_residual(g, self.w_out, ctx.residual):        # the product adds into the residual stream itself
+            return None
         return Delta(ops.linear(g, self.w_out, None, None, out_dtype=torch.float32))
 
 

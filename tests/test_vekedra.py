@@ -207,6 +207,41 @@ def test_routing_and_experts(dtype):
         assert (out.double().cpu() - ref).abs().max() < tol * max(1.0, ref.abs().max())
 
 
+@pytest.mark.parametrize("W, F, E, top, rows", [(64, 40, 5, 2, 200), (72, 16, 3, 1, 70), (32, 24, 9, 3, 333), (128, 96, 4, 2, 64)])
+def test_routed_tiles_for_many_rows(W, F, E, top, rows):
+    """Rows sorted by expert and run in tiles on the tensor cores (bfloat16): against the plain implementation, and
+    the same rows in another order and beside other rows give the same bits (a row's result is its own)."""
+    from cbis_b200.kernels import ops
+    g = torch.Generator().manual_seed(rows)
+    h = dev(torch.randn(rows, W, generator=g), "bfloat16")
+    router = dev(torch.randn(E, W, generator=g), "bfloat16")
+    if E == 4:
+        router[1:] = 0                                   # nearly every row goes to experts 0 and one more: long runs of tiles
+    gate_up = dev(torch.randn(E, 2 * F, W, generator=g) / W ** 0.5, "bfloat16")
+    down = dev(torch.randn(E, W, F, generator=g) / F ** 0.5, "bfloat16")
+
+    def run(x, accumulate_into=None):
+        n = x.shape[0]
+        ids = torch.empty(n, top, dtype=torch.int32, device="cuda")
+        wts = torch.empty(n, top, dtype=torch.float32, device="cuda")
+        ops.route_topk(x, router, top, "sigmoid", False, ids, wts)
+        out = accumulate_into if accumulate_into is not None else torch.empty(n, W, dtype=torch.float32, device="cuda")
+        assert ops.routed_tiles_takes(x, gate_up, down)
+        ops.routed_tiles(x, gate_up, down, ids, wts, "silu", True, out, accumulate=accumulate_into is not None)
+        return out
+    out = run(h)
+    experts = [(gate_up[e, :F].double().cpu(), gate_up[e, F:].double().cpu(), down[e].double().cpu()) for e in range(E)]
+    ref = pv.routed_experts(h.double().cpu(), router.double().cpu(), experts, top)
+    assert (out.double().cpu() - ref).abs().max() < 3e-2 * max(1.0, ref.abs().max())
+    perm = torch.randperm(rows, generator=g).cuda()
+    assert torch.equal(run(h[perm].contiguous()), out[perm])
+    more = torch.cat([dev(torch.randn(50, W, generator=g), "bfloat16"), h])
+    assert torch.equal(run(more)[50:], out)
+    base = torch.randn(rows, W, generator=g).cuda()
+    added = run(h, accumulate_into=base.clone())
+    assert (added - (base + out)).abs().max() < 1e-5
+
+
 # ---- single mechanisms and whole models through the engine -----------------------------------------------------
 ALONE = {
     "latent": config(32, 50, [latent(2, 8, 12, 16, 6, 0.35, mlp=None)]),
@@ -365,7 +400,8 @@ def test_far_tokens_held_by_the_state():
             if dtype == "float32":
                 assert err.max() < 1e-4, (sizes, err.max().item())
             else:
-                assert err.max() < tolerance(dtype, ref), (sizes, err.max().item())
+                tol = tolerance(dtype, ref)
+                assert err.max() < 2 * tol and err.median() < tol / 4, (sizes, err.max().item(), err.median().item())
 
 
 # ---- generation through the scheduler --------------------------------------------------------------------------
