@@ -600,11 +600,18 @@ def vekedra_kernels(torch, ops, pk):
 
             def run():
                 ops.route_topk(h, router, top, "sigmoid", False, ids, wt)
-                ops.routed_gate_up(h, gu, ids, wt, "silu", True, hid)
-                ops.routed_down(hid, dn, ids, wt, True, o)
+                if ops.routed_tiles_takes(h, gu, dn):          # as the part chooses
+                    ops.routed_tiles(h, gu, dn, ids, wt, "silu", True, o)
+                else:
+                    ops.routed_gate_up(h, gu, ids, wt, "silu", True, hid)
+                    ops.routed_down(hid, dn, ids, wt, True, o)
             return run
         touched = min(E, rows * top)
         timed(experts, touched * 3 * F * W * 2 + rows * W * 6, f"routed_feed_forward_{tag}", copies=2)
+        if rows > 64:
+            flops = 2.0 * rows * top * 3 * F * W
+            us = out[f"routed_feed_forward_{tag}"]["us"]
+            out[f"routed_feed_forward_{tag}"]["frac_of_bf16_peak"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
     return out
 
 

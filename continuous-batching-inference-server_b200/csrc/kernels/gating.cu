@@ -9,9 +9,11 @@ namespace cbis {
 
 // grid (rows, parts); part g of row r covers columns g*pw .. g*pw + pw - 1.
 //   v = x[r, c] * (gate ? act(gate[r, c]) : 1);  out[r, c] = v / sqrt(mean_c(v^2) + eps) * (weight ? weight[c] : 1)
+// With `staged` the part's v wait in shared memory (pw floats) between the two passes; else they are read again.
 template <typename TI, typename TG, typename TO>
 __global__ void rms_norm_kernel(const TI* x, int x_ld, const TG* gate, int gate_ld, int gate_act,
-                                const float* __restrict__ weight, float eps, TO* out, int out_ld, int pw) {
+                                const float* __restrict__ weight, float eps, TO* out, int out_ld, int pw, int staged) {
+  extern __shared__ float vs[];
   __shared__ float red[33];
   pdl_trigger();
   pdl_wait();
@@ -22,13 +24,19 @@ __global__ void rms_norm_kernel(const TI* x, int x_ld, const TG* gate, int gate_
   for (int c = threadIdx.x; c < pw; c += blockDim.x) {
     float v = to_f32(xr[c]);
     if (gr) v *= activate(to_f32(gr[c]), gate_act);
+    if (staged) vs[c] = v;
     ss += v * v;
   }
   const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)pw + eps);
   TO* orow = out + (size_t)r * out_ld + c0;
   for (int c = threadIdx.x; c < pw; c += blockDim.x) {
-    float v = to_f32(xr[c]);
-    if (gr) v *= activate(to_f32(gr[c]), gate_act);
+    float v;
+    if (staged) {
+      v = vs[c];
+    } else {
+      v = to_f32(xr[c]);
+      if (gr) v *= activate(to_f32(gr[c]), gate_act);
+    }
     v *= inv;
     if (weight) v *= weight[c0 + c];
     from_f32(orow[c], v);
@@ -53,8 +61,10 @@ template <typename TI, typename TG, typename TO>
 static int launch_rms(const void* x, int x_ld, const void* gate, int gate_ld, int gate_act, const float* weight,
                       float eps, void* out, int out_ld, int rows, int parts, int pw, cudaStream_t st) {
   const int threads = pw >= 2048 ? 512 : (pw >= 512 ? 256 : (pw >= 128 ? 128 : 64));
-  return (int)launch_pdl(rms_norm_kernel<TI, TG, TO>, dim3(rows, parts), dim3(threads), 0, st, (const TI*)x, x_ld,
-                         (const TG*)gate, gate_ld, gate_act, weight, eps, (TO*)out, out_ld, pw);
+  const int staged = pw <= 10240 ? 1 : 0;         // 40 KB of shared memory at most
+  return (int)launch_pdl(rms_norm_kernel<TI, TG, TO>, dim3(rows, parts), dim3(threads),
+                         staged ? (size_t)pw * sizeof(float) : 0, st, (const TI*)x, x_ld, (const TG*)gate, gate_ld,
+                         gate_act, weight, eps, (TO*)out, out_ld, pw, staged);
 }
 
 }  // namespace cbis

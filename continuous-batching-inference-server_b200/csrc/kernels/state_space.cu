@@ -12,11 +12,12 @@
 namespace cbis {
 
 constexpr int kMaxTaps = 8;
-constexpr int kConvRows = 64;      // rows of a segment that one block of the convolution walks
+constexpr int kConvRows = 32;      // rows of a segment that one block of the convolution walks
 
 // grid (ceil(C / 128), S, ceil(max rows of a segment / kConvRows)), 128 threads: one channel each.
 // u = in[r, c0 + c]; out[r, c] = act(bias[c] + sum_j w[c, j] * u[t - (K-1) + j]), j = 0..K-1.
 // state[slot][j][c], j = 0..K-2, holds the input K-1-j rows before the segment's first row.
+// The taps sit right-aligned in a window of kMaxTaps (absent taps weigh nothing), so no index depends on K.
 template <typename TT>
 __global__ void __launch_bounds__(128)
 causal_conv_act_kernel(const TT* in, int in_ld, int c0, const float* __restrict__ w, const float* __restrict__ bias,
@@ -31,31 +32,41 @@ causal_conv_act_kernel(const TT* in, int in_ld, int c0, const float* __restrict_
   if (c >= C || first >= n) return;
   const int last = min(n, first + kConvRows);
   const float* st = state + (long long)seg_slot[s] * slot_stride;
-  float wk[kMaxTaps], hist[kMaxTaps];
+  constexpr int M = kMaxTaps;
+  float wk[M], hist[M - 1];
 #pragma unroll
-  for (int j = 0; j < kMaxTaps; ++j) wk[j] = j < K ? w[(size_t)c * K + j] : 0.f;
+  for (int j = 0; j < M; ++j) {
+    const int tap = j - (M - K);                 // window place j holds tap j - (M - K)
+    wk[j] = tap >= 0 ? w[(size_t)c * K + tap] : 0.f;
+  }
   const float b = bias ? bias[c] : 0.f;
-  // hist[j], j < K-1: the input (K-1-j) rows before row `first`
+  // hist[j]: the input (M-1-j) rows before row `first`; only the last K-1 of them are ever weighed
 #pragma unroll
-  for (int j = 0; j < kMaxTaps - 1; ++j) {
+  for (int j = 0; j < M - 1; ++j) {
     hist[j] = 0.f;
-    if (j < K - 1) {
-      const int i = first - (K - 1) + j;      // index inside the segment; negative: before this step
+    const int back = M - 1 - j;                  // rows before `first`
+    if (back <= K - 1) {
+      const int i = first - back;                // index inside the segment; negative: before this step
       hist[j] = i >= 0 ? to_f32(in[(size_t)(row0 + i) * in_ld + c0 + c]) : st[(size_t)(K - 1 + i) * C + c];
     }
   }
-  for (int i = first; i < last; ++i) {
-    const float cur = to_f32(in[(size_t)(row0 + i) * in_ld + c0 + c]);
-    float acc = b;
+  for (int i0 = first; i0 < last; i0 += 8) {
+    float cur[8];
 #pragma unroll
-    for (int j = 0; j < kMaxTaps - 1; ++j)
-      if (j < K - 1) acc = fmaf(wk[j], hist[j], acc);
-    acc = fmaf(wk[K - 1], cur, acc);
-    from_f32(out[(size_t)(row0 + i) * out_ld + c], activate(acc, act));
+    for (int u = 0; u < 8; ++u) cur[u] = i0 + u < last ? to_f32(in[(size_t)(row0 + i0 + u) * in_ld + c0 + c]) : 0.f;
 #pragma unroll
-    for (int j = 0; j < kMaxTaps - 2; ++j)
-      if (j < K - 2) hist[j] = hist[j + 1];
-    if (K >= 2) hist[K - 2] = cur;
+    for (int u = 0; u < 8; ++u) {
+      if (i0 + u < last) {
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < M - 1; ++j) acc = fmaf(wk[j], hist[j], acc);
+        acc = fmaf(wk[M - 1], cur[u], acc);
+        from_f32(out[(size_t)(row0 + i0 + u) * out_ld + c], activate(acc, act));
+#pragma unroll
+        for (int j = 0; j < M - 2; ++j) hist[j] = hist[j + 1];
+        hist[M - 2] = cur[u];
+      }
+    }
   }
 }
 
@@ -87,24 +98,34 @@ conv_state_update_kernel(const TT* in, int in_ld, int c0, float* state, long lon
 
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+constexpr int kScanTokens = 16;     // rows of a segment staged in shared memory at a time
+
 // grid (ceil(P / 32), H, S), 256 threads: thread t owns column p = 32 * blockIdx.x + t / 8 of the head's state and
 // the states n = t % 8 + 8 i, i < NPL, of that column; the eight lanes of a column add their shares of y by shuffles.
 // State of a slot: S[h][p][n].  xbc row: x (H*P) | B (G*N) | C (G*N); the raw step sizes are H columns of `proj`.
+// The rows are walked 16 at a time: B, C and x of 16 rows wait in shared memory, with the step size dt and
+// expm1(-exp(A_log) dt) of each row computed once for the block; the next 16 rows' loads are in flight meanwhile.
 template <typename TT, int NPL>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_off, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ Dskip, float* state, long long slot_stride,
                 const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H, int P, int N, int G) {
+  constexpr int NP = 8 * NPL;                       // the state size rounded up
+  constexpr int TC = kScanTokens;
+  constexpr int BC_PER_THREAD = TC * 2 * NP / 256;  // = NPL
+  __shared__ float bc[TC * 2 * NP];                 // [row][B | C][n]
+  __shared__ float xs[TC * 32];                     // [row][column of this block]
+  __shared__ float dts[TC], dm1s[TC];
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.y, s = blockIdx.z;
   const int row0 = cu_rows[s], n_rows = cu_rows[s + 1] - row0;
   if (n_rows <= 0) return;
-  const int nl = threadIdx.x & 7;
-  const int p = blockIdx.x * 32 + (threadIdx.x >> 3);
+  const int nl = threadIdx.x & 7, pl = threadIdx.x >> 3;
+  const int p = blockIdx.x * 32 + pl;
   const bool live = p < P;
   const int g = h / (H / G);
-  const int x_col = h * P + (live ? p : 0);
+  const int x_col0 = h * P + blockIdx.x * 32;
   const int b_col = H * P + g * N, c_col = H * P + G * N + g * N;
   float* sp = state + (long long)seg_slot[s] * slot_stride + ((size_t)h * P + (live ? p : 0)) * N;
   float S[NPL];
@@ -114,48 +135,60 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
     S[i] = (live && n < N) ? sp[n] : 0.f;
   }
   const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
-  // the next row's operands are fetched while this row's recurrence runs
-  float xv, dtr, Bv[NPL], Cv[NPL];
-  auto fetch = [&](int r, float& x_, float& dt_, float (&B_)[NPL], float (&C_)[NPL]) {
-    const TT* row = xbc + (size_t)r * xbc_ld;
-    x_ = to_f32(row[x_col]);
-    dt_ = to_f32(proj[(size_t)r * proj_ld + dt_off + h]);
+
+  // what this thread fetches of a chunk of rows: NPL values of B | C, two of x, and (the first TC threads) a step size
+  float r_bc[BC_PER_THREAD], r_x[2], r_dt = 0.f;
+  auto fetch = [&](int first) {
+    const int tc = min(TC, n_rows - first);
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int n = nl + 8 * i;
-      B_[i] = n < N ? to_f32(row[b_col + n]) : 0.f;
-      C_[i] = n < N ? to_f32(row[c_col + n]) : 0.f;
+    for (int j = 0; j < BC_PER_THREAD; ++j) {
+      const int idx = threadIdx.x + 256 * j, t = idx / (2 * NP), rem = idx % (2 * NP), n = rem % NP;
+      r_bc[j] = (t < tc && n < N) ? to_f32(xbc[(size_t)(row0 + first + t) * xbc_ld + (rem < NP ? b_col : c_col) + n]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int idx = threadIdx.x + 256 * j, t = idx >> 5, c = idx & 31;
+      r_x[j] = (t < tc && blockIdx.x * 32 + c < P) ? to_f32(xbc[(size_t)(row0 + first + t) * xbc_ld + x_col0 + c]) : 0.f;
+    }
+    if (threadIdx.x < TC)
+      r_dt = threadIdx.x < tc ? to_f32(proj[(size_t)(row0 + first + threadIdx.x) * proj_ld + dt_off + h]) : 0.f;
+  };
+  auto stage = [&]() {
+#pragma unroll
+    for (int j = 0; j < BC_PER_THREAD; ++j) bc[threadIdx.x + 256 * j] = r_bc[j];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) xs[threadIdx.x + 256 * j] = r_x[j];
+    if (threadIdx.x < TC) {
+      const float dt = softplus_f32(r_dt + bias);
+      dts[threadIdx.x] = dt;
+      // The decay is applied as S += (decay - 1) S with decay - 1 = expm1(-exp(A_log) dt): a decay close to 1 rounded
+      // to a float just below 1 loses most of the digits of 1 - decay, the same way at every step when the step size
+      // barely changes, and a state that is read a thousand tokens later would carry a thousand times that error.
+      dm1s[threadIdx.x] = expm1f(neg_a * dt);
     }
   };
-  fetch(row0, xv, dtr, Bv, Cv);
-  for (int i_row = 0; i_row < n_rows; ++i_row) {
-    const int r = row0 + i_row;
-    float xn = 0.f, dtn = 0.f, Bn[NPL], Cn[NPL];
-    if (i_row + 1 < n_rows) fetch(r + 1, xn, dtn, Bn, Cn);
-    const float dt = softplus_f32(dtr + bias);
-    // The decay is applied as S += (decay - 1) S with decay - 1 = expm1(-exp(A_log) dt): a decay close to 1 rounded
-    // to a float just below 1 loses most of the digits of 1 - decay, the same way at every step when the step size
-    // barely changes, and a state that is read a thousand tokens later would carry a thousand times that error.
-    const float decay_m1 = expm1f(neg_a * dt);
-    const float dx = dt * xv;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      S[i] = fmaf(decay_m1, S[i], fmaf(Bv[i], dx, S[i]));
-      acc = fmaf(S[i], Cv[i], acc);
-    }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-    if (live && nl == 0) y[(size_t)r * y_ld + h * P + p] = fmaf(dskip, xv, acc);
-    if (i_row + 1 < n_rows) {
-      xv = xn;
-      dtr = dtn;
+  fetch(0);
+  for (int first = 0; first < n_rows; first += TC) {
+    __syncthreads();                 // the rows staged before have been used
+    stage();
+    __syncthreads();
+    if (first + TC < n_rows) fetch(first + TC);
+    const int tc = min(TC, n_rows - first);
+#pragma unroll 4
+    for (int t = 0; t < tc; ++t) {
+      const float xv = xs[t * 32 + pl];
+      const float dx = dts[t] * xv, decay_m1 = dm1s[t];
+      const float* Bt = bc + t * 2 * NP + nl;
+      float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
-        Bv[i] = Bn[i];
-        Cv[i] = Cn[i];
+        S[i] = fmaf(decay_m1, S[i], fmaf(Bt[8 * i], dx, S[i]));
+        acc = fmaf(S[i], Bt[NP + 8 * i], acc);
       }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (live && nl == 0) y[(size_t)(row0 + first + t) * y_ld + h * P + p] = fmaf(dskip, xv, acc);
     }
   }
   if (live) {
