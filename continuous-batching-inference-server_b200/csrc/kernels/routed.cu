@@ -231,26 +231,42 @@ routed_tiles_kernel(const __nv_bfloat16* A, int a_ld, const __nv_bfloat16* __res
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int k0 = 0; k0 < K; k0 += kTileK) {
-    // 64 rows x 32 columns = 256 pieces of 16 bytes per matrix, two per thread
+  // 64 rows x 32 columns = 256 pieces of 16 bytes per matrix, two per thread; the pieces of the NEXT 32 columns are
+  // fetched into registers while the tensor cores work on the ones in shared memory
+  constexpr int NB = DUAL ? 2 : 1;
+  uint4 ra[2], rb[NB][2];
+  const __nv_bfloat16* a_src[2];
+  const __nv_bfloat16* b_src[2];
+  int piece_k[2];
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int idx = threadIdx.x + it * 128, r = idx >> 2;
+    piece_k[it] = (idx & 3) * 8;
+    const int pair = pair_of[r];
+    a_src[it] = pair >= 0 ? A + (size_t)(DUAL ? pair / top : pair) * a_ld : nullptr;
+    b_src[it] = n0 + r < N ? B0 + (size_t)(n0 + r) * K : nullptr;
+  }
+  auto fetch = [&](int k0) {
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
-      const int idx = threadIdx.x + it * 128, r = idx >> 2, kc = (idx & 3) * 8;
-      const bool k_ok = k0 + kc < K;
-      const int pair = pair_of[r];
-      uint4 v = zero;
-      if (pair >= 0 && k_ok) v = *reinterpret_cast<const uint4*>(A + (size_t)(DUAL ? pair / top : pair) * a_ld + k0 + kc);
-      *reinterpret_cast<uint4*>(&As[r][kc]) = v;
-      const bool n_ok = n0 + r < N && k_ok;
-      v = zero;
-      if (n_ok) v = *reinterpret_cast<const uint4*>(B0 + (size_t)(n0 + r) * K + k0 + kc);
-      *reinterpret_cast<uint4*>(&Bs[0][r][kc]) = v;
-      if (DUAL) {
-        v = zero;
-        if (n_ok) v = *reinterpret_cast<const uint4*>(B0 + (size_t)(N + n0 + r) * K + k0 + kc);
-        *reinterpret_cast<uint4*>(&Bs[DUAL ? 1 : 0][r][kc]) = v;
-      }
+      const int k = k0 + piece_k[it];
+      const bool k_ok = k < K;
+      ra[it] = (a_src[it] && k_ok) ? *reinterpret_cast<const uint4*>(a_src[it] + k) : zero;
+#pragma unroll
+      for (int m = 0; m < NB; ++m)
+        rb[m][it] = (b_src[it] && k_ok) ? *reinterpret_cast<const uint4*>(b_src[it] + (size_t)m * N * K + k) : zero;
     }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += kTileK) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int r = (threadIdx.x + it * 128) >> 2;
+      *reinterpret_cast<uint4*>(&As[r][piece_k[it]]) = ra[it];
+#pragma unroll
+      for (int m = 0; m < NB; ++m) *reinterpret_cast<uint4*>(&Bs[m][r][piece_k[it]]) = rb[m][it];
+    }
+    if (k0 + kTileK < K) fetch(k0 + kTileK);
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < kTileK; kk += 16) {

@@ -100,44 +100,64 @@ __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : l
 
 constexpr int kScanTokens = 16;     // rows of a segment staged in shared memory at a time
 
-// grid (ceil(P / 32), H, S), 256 threads: thread t owns column p = 32 * blockIdx.x + t / 8 of the head's state and
-// the states n = t % 8 + 8 i, i < NPL, of that column; the eight lanes of a column add their shares of y by shuffles.
+// grid (ceil(P / CB), H, S), 256 threads, CB = 256 / L columns of one head's state a block: thread t owns column
+// p = CB * blockIdx.x + t / L and the states n = (t % L) * NPL + i, i < NPL, of that column; the L lanes of a column add
+// their shares of y by shuffles.  L is 8 where the step has blocks enough, 16 where few segments (one long prompt)
+// would leave most of the machine idle: the state's values do not depend on L, y's last bit may.
 // State of a slot: S[h][p][n].  xbc row: x (H*P) | B (G*N) | C (G*N); the raw step sizes are H columns of `proj`.
 // The rows are walked 16 at a time: B, C and x of 16 rows wait in shared memory, with the step size dt and
 // expm1(-exp(A_log) dt) of each row computed once for the block; the next 16 rows' loads are in flight meanwhile.
-template <typename TT, int NPL>
+// In shared memory a lane's NPL values of B (and of C) are followed by four unused floats, so the lanes' 16-byte
+// loads fall into different banks.
+template <typename TT, int NPL, int L>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_off, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ Dskip, float* state, long long slot_stride,
                 const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H, int P, int N, int G) {
-  constexpr int NP = 8 * NPL;                       // the state size rounded up
+  constexpr int NP = L * NPL;                       // the state size rounded up
   constexpr int TC = kScanTokens;
-  constexpr int BC_PER_THREAD = TC * 2 * NP / 256;  // = NPL
-  __shared__ float bc[TC * 2 * NP];                 // [row][B | C][n]
-  __shared__ float xs[TC * 32];                     // [row][column of this block]
+  constexpr int CB = 256 / L;                       // columns a block
+  constexpr int BC_PER_THREAD = TC * 2 * NP / 256;
+  constexpr int X_PER_THREAD = (TC * CB + 255) / 256;
+  constexpr int LS = NPL + (NPL >= 4 ? 4 : 0);      // a lane's stretch of a row of B or C, padded
+  __shared__ __align__(16) float bc[TC * 2 * L * LS];   // [row][B | C][lane][LS]
+  __shared__ float xs[TC * CB];                     // [row][column of this block]
   __shared__ float dts[TC], dm1s[TC];
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.y, s = blockIdx.z;
   const int row0 = cu_rows[s], n_rows = cu_rows[s + 1] - row0;
   if (n_rows <= 0) return;
-  const int nl = threadIdx.x & 7, pl = threadIdx.x >> 3;
-  const int p = blockIdx.x * 32 + pl;
+  const int nl = threadIdx.x % L, pl = threadIdx.x / L;
+  const int p = blockIdx.x * CB + pl;
   const bool live = p < P;
   const int g = h / (H / G);
-  const int x_col0 = h * P + blockIdx.x * 32;
+  const int x_col0 = h * P + blockIdx.x * CB;
   const int b_col = H * P + g * N, c_col = H * P + G * N + g * N;
   float* sp = state + (long long)seg_slot[s] * slot_stride + ((size_t)h * P + (live ? p : 0)) * N;
   float S[NPL];
+  // a lane's states lie side by side: 16-byte loads and stores where the row of states allows them
+  const bool vec = NPL >= 4 && N == NP && !((uintptr_t)sp & 15);
+  if (vec) {
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int n = nl + 8 * i;
-    S[i] = (live && n < N) ? sp[n] : 0.f;
+    for (int i = 0; i < NPL; i += 4) {
+      const float4 v = live ? *reinterpret_cast<const float4*>(sp + nl * NPL + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      S[i] = v.x;
+      if (i + 1 < NPL) S[i + 1] = v.y;
+      if (i + 2 < NPL) S[i + 2] = v.z;
+      if (i + 3 < NPL) S[i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = nl * NPL + i;
+      S[i] = (live && n < N) ? sp[n] : 0.f;
+    }
   }
   const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
 
-  // what this thread fetches of a chunk of rows: NPL values of B | C, two of x, and (the first TC threads) a step size
-  float r_bc[BC_PER_THREAD], r_x[2], r_dt = 0.f;
+  // what this thread fetches of a chunk of rows: values of B | C, of x, and (the first TC threads) a step size
+  float r_bc[BC_PER_THREAD], r_x[X_PER_THREAD], r_dt = 0.f;
   auto fetch = [&](int first) {
     const int tc = min(TC, n_rows - first);
 #pragma unroll
@@ -146,18 +166,22 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
       r_bc[j] = (t < tc && n < N) ? to_f32(xbc[(size_t)(row0 + first + t) * xbc_ld + (rem < NP ? b_col : c_col) + n]) : 0.f;
     }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int idx = threadIdx.x + 256 * j, t = idx >> 5, c = idx & 31;
-      r_x[j] = (t < tc && blockIdx.x * 32 + c < P) ? to_f32(xbc[(size_t)(row0 + first + t) * xbc_ld + x_col0 + c]) : 0.f;
+    for (int j = 0; j < X_PER_THREAD; ++j) {
+      const int idx = threadIdx.x + 256 * j, t = idx / CB, c = idx % CB;
+      r_x[j] = (t < tc && blockIdx.x * CB + c < P) ? to_f32(xbc[(size_t)(row0 + first + t) * xbc_ld + x_col0 + c]) : 0.f;
     }
     if (threadIdx.x < TC)
       r_dt = threadIdx.x < tc ? to_f32(proj[(size_t)(row0 + first + threadIdx.x) * proj_ld + dt_off + h]) : 0.f;
   };
   auto stage = [&]() {
 #pragma unroll
-    for (int j = 0; j < BC_PER_THREAD; ++j) bc[threadIdx.x + 256 * j] = r_bc[j];
+    for (int j = 0; j < BC_PER_THREAD; ++j) {
+      const int idx = threadIdx.x + 256 * j, n = idx % NP;      // idx = (row * 2 + B|C) * NP + n
+      bc[(idx / NP * L + n / NPL) * LS + n % NPL] = r_bc[j];
+    }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) xs[threadIdx.x + 256 * j] = r_x[j];
+    for (int j = 0; j < X_PER_THREAD; ++j)
+      if (threadIdx.x + 256 * j < TC * CB) xs[threadIdx.x + 256 * j] = r_x[j];
     if (threadIdx.x < TC) {
       const float dt = softplus_f32(r_dt + bias);
       dts[threadIdx.x] = dt;
@@ -176,25 +200,47 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
     const int tc = min(TC, n_rows - first);
 #pragma unroll 4
     for (int t = 0; t < tc; ++t) {
-      const float xv = xs[t * 32 + pl];
+      const float xv = xs[t * CB + pl];
       const float dx = dts[t] * xv, decay_m1 = dm1s[t];
-      const float* Bt = bc + t * 2 * NP + nl;
+      const float* Bt = bc + (t * 2 * L + nl) * LS;
+      const float* Ct = Bt + L * LS;
       float acc = 0.f;
+      if constexpr (NPL >= 4) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;       // four short chains of sums instead of one long one
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) {
-        S[i] = fmaf(decay_m1, S[i], fmaf(Bt[8 * i], dx, S[i]));
-        acc = fmaf(S[i], Bt[NP + 8 * i], acc);
+        for (int i = 0; i < NPL; i += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(Bt + i), c4 = *reinterpret_cast<const float4*>(Ct + i);
+          S[i] = fmaf(decay_m1, S[i], fmaf(b4.x, dx, S[i]));
+          S[i + 1] = fmaf(decay_m1, S[i + 1], fmaf(b4.y, dx, S[i + 1]));
+          S[i + 2] = fmaf(decay_m1, S[i + 2], fmaf(b4.z, dx, S[i + 2]));
+          S[i + 3] = fmaf(decay_m1, S[i + 3], fmaf(b4.w, dx, S[i + 3]));
+          a0 = fmaf(S[i], c4.x, a0);
+          a1 = fmaf(S[i + 1], c4.y, a1);
+          a2 = fmaf(S[i + 2], c4.z, a2);
+          a3 = fmaf(S[i + 3], c4.w, a3);
+        }
+        acc = (a0 + a1) + (a2 + a3);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+          S[i] = fmaf(decay_m1, S[i], fmaf(Bt[i], dx, S[i]));
+          acc = fmaf(S[i], Ct[i], acc);
+        }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+#pragma unroll
+      for (int o = 1; o < L; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (live && nl == 0) y[(size_t)(row0 + first + t) * y_ld + h * P + p] = fmaf(dskip, xv, acc);
     }
   }
-  if (live) {
+  if (live && vec) {
+#pragma unroll
+    for (int i = 0; i < NPL; i += 4)
+      *reinterpret_cast<float4*>(sp + nl * NPL + i) =
+          make_float4(S[i], S[i + 1 < NPL ? i + 1 : i], S[i + 2 < NPL ? i + 2 : i], S[i + 3 < NPL ? i + 3 : i]);
+  } else if (live) {
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
-      const int n = nl + 8 * i;
+      const int n = nl * NPL + i;
       if (n < N) sp[n] = S[i];
     }
   }
@@ -204,16 +250,26 @@ template <typename TT>
 static int launch_scan(const void* xbc, int xbc_ld, const void* proj, int proj_ld, int dt_off, const float* dt_bias,
                        const float* A_log, const float* D, float* state, long long slot_stride, const int* seg_slot,
                        const int* cu_rows, float* y, int y_ld, int S, int H, int P, int N, int G, cudaStream_t st) {
-  const dim3 grid((P + 31) / 32, H, S), block(256);
-#define CBIS_SCAN(NPL)                                                                                             \
-  return (int)launch_pdl(ssm_scan_kernel<TT, NPL>, grid, block, 0, st, (const TT*)xbc, xbc_ld, (const TT*)proj, proj_ld, \
-                         dt_off, dt_bias, A_log, D, state, slot_stride, seg_slot, cu_rows, y, y_ld, H, P, N, G)
-  if (N <= 8) CBIS_SCAN(1);
-  if (N <= 16) CBIS_SCAN(2);
-  if (N <= 32) CBIS_SCAN(4);
-  if (N <= 64) CBIS_SCAN(8);
-  if (N <= 128) CBIS_SCAN(16);
-  if (N <= 256) CBIS_SCAN(32);
+  // lanes a column: 8, or 16 while the warps (segments x heads x columns x lanes / 32) would not give every SM its
+  // sixteen.  Not 32: the blocks of one long prompt (every one walks the whole prompt) must all run at once, and 512
+  // blocks of 33 KB of shared memory do not (measured: 32 lanes took twice as long as 8).
+  int L = 8;
+  if ((long long)S * H * P * L / 32 < 148 * 16 && N >= 64) L = 16;
+#define CBIS_SCAN(NPL, LL)                                                                                          \
+  return (int)launch_pdl(ssm_scan_kernel<TT, NPL, LL>, dim3((P + 256 / LL - 1) / (256 / LL), H, S), dim3(256), 0, st, \
+                         (const TT*)xbc, xbc_ld, (const TT*)proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride, \
+                         seg_slot, cu_rows, y, y_ld, H, P, N, G)
+  if (L == 16) {
+    if (N <= 64) CBIS_SCAN(4, 16);
+    if (N <= 128) CBIS_SCAN(8, 16);
+    if (N <= 256) CBIS_SCAN(16, 16);
+  }
+  if (N <= 8) CBIS_SCAN(1, 8);
+  if (N <= 16) CBIS_SCAN(2, 8);
+  if (N <= 32) CBIS_SCAN(4, 8);
+  if (N <= 64) CBIS_SCAN(8, 8);
+  if (N <= 128) CBIS_SCAN(16, 8);
+  if (N <= 256) CBIS_SCAN(32, 8);
 #undef CBIS_SCAN
   return CBIS_ERR_TOO_LARGE;
 }
