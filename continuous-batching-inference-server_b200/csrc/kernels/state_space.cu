@@ -96,6 +96,12 @@ conv_state_update_kernel(const TT* in, int in_ld, int c0, float* state, long lon
     if (j < K - 1) st[(size_t)j * C + c] = next[j];
 }
 
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 constexpr int kScanTokens = 16;     // rows of a segment staged in shared memory at a time
@@ -113,7 +119,7 @@ template <typename TT, int NPL, int L>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_off, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ Dskip, float* state, long long slot_stride,
-                const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H, int P, int N, int G) {
+                const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H, int P, int N, int G, int use_async) {
   constexpr int NP = L * NPL;                       // the state size rounded up
   constexpr int TC = kScanTokens;
   constexpr int CB = 256 / L;                       // columns a block
@@ -123,6 +129,12 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
   __shared__ __align__(16) float bc[TC * 2 * L * LS];   // [row][B | C][lane][LS]
   __shared__ float xs[TC * CB];                     // [row][column of this block]
   __shared__ float dts[TC], dm1s[TC];
+  // with `use_async` (every run of B, C and x starts on 16 bytes): the next rows arrive here by cp.async while this
+  // block works, as they are stored; they are converted and spread into `bc` and `xs` when their turn comes
+  constexpr bool kAsyncFits = NP <= 128;            // beyond that the static 48 KB of shared memory do not hold both
+  __shared__ __align__(16) TT raw_bc[kAsyncFits ? TC * 2 * NP : 8];  // [row][B | C][n]
+  __shared__ __align__(16) TT raw_x[TC * CB];
+  if (!kAsyncFits) use_async = 0;
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.y, s = blockIdx.z;
@@ -157,9 +169,26 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
   const float neg_a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
 
   // what this thread fetches of a chunk of rows: values of B | C, of x, and (the first TC threads) a step size
+  constexpr int E16 = 16 / (int)sizeof(TT);         // elements of a 16-byte piece
   float r_bc[BC_PER_THREAD], r_x[X_PER_THREAD], r_dt = 0.f;
   auto fetch = [&](int first) {
     const int tc = min(TC, n_rows - first);
+    if (threadIdx.x < TC)
+      r_dt = threadIdx.x < tc ? to_f32(proj[(size_t)(row0 + first + threadIdx.x) * proj_ld + dt_off + h]) : 0.f;
+    if (use_async) {
+      for (int piece = threadIdx.x; piece < TC * 2 * NP / E16; piece += 256) {
+        const int idx = piece * E16, t = idx / (2 * NP), rem = idx % (2 * NP), n = rem % NP;
+        if (t < tc && n < N)
+          cp_async_16(raw_bc + idx, xbc + (size_t)(row0 + first + t) * xbc_ld + (rem < NP ? b_col : c_col) + n);
+      }
+      for (int piece = threadIdx.x; piece < TC * CB / E16; piece += 256) {
+        const int idx = piece * E16, t = idx / CB, c = idx % CB;
+        if (t < tc && blockIdx.x * CB + c < P)
+          cp_async_16(raw_x + idx, xbc + (size_t)(row0 + first + t) * xbc_ld + x_col0 + c);
+      }
+      cp_async_commit();
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < BC_PER_THREAD; ++j) {
       const int idx = threadIdx.x + 256 * j, t = idx / (2 * NP), rem = idx % (2 * NP), n = rem % NP;
@@ -170,10 +199,23 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
       const int idx = threadIdx.x + 256 * j, t = idx / CB, c = idx % CB;
       r_x[j] = (t < tc && blockIdx.x * CB + c < P) ? to_f32(xbc[(size_t)(row0 + first + t) * xbc_ld + x_col0 + c]) : 0.f;
     }
-    if (threadIdx.x < TC)
-      r_dt = threadIdx.x < tc ? to_f32(proj[(size_t)(row0 + first + threadIdx.x) * proj_ld + dt_off + h]) : 0.f;
   };
-  auto stage = [&]() {
+  auto stage = [&](int first) {
+    if (use_async) {
+      const int tc = min(TC, n_rows - first);
+      cp_async_wait_all();
+      __syncthreads();               // every thread's pieces have arrived
+#pragma unroll
+      for (int j = 0; j < BC_PER_THREAD; ++j) {
+        const int idx = threadIdx.x + 256 * j, n = idx % NP;
+        r_bc[j] = (idx / (2 * NP) < tc && n < N) ? to_f32(raw_bc[idx]) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < X_PER_THREAD; ++j) {
+        const int idx = threadIdx.x + 256 * j;
+        r_x[j] = (idx < TC * CB && idx / CB < tc && blockIdx.x * CB + idx % CB < P) ? to_f32(raw_x[idx]) : 0.f;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < BC_PER_THREAD; ++j) {
       const int idx = threadIdx.x + 256 * j, n = idx % NP;      // idx = (row * 2 + B|C) * NP + n
@@ -194,8 +236,8 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
   fetch(0);
   for (int first = 0; first < n_rows; first += TC) {
     __syncthreads();                 // the rows staged before have been used
-    stage();
-    __syncthreads();
+    stage(first);
+    __syncthreads();                 // (and the raw rows have been read: the next ones may overwrite them)
     if (first + TC < n_rows) fetch(first + TC);
     const int tc = min(TC, n_rows - first);
 #pragma unroll 4
@@ -255,10 +297,14 @@ static int launch_scan(const void* xbc, int xbc_ld, const void* proj, int proj_l
   // blocks of 33 KB of shared memory do not (measured: 32 lanes took twice as long as 8).
   int L = 8;
   if ((long long)S * H * P * L / 32 < 148 * 16 && N >= 64) L = 16;
+  // rows may come by cp.async where every run of B, C and x of a row starts on 16 bytes
+  const int e16 = 16 / (int)sizeof(TT);
+  const int use_async = (N % e16 == 0 && P % e16 == 0 && (H * P) % e16 == 0 && xbc_ld % e16 == 0 &&
+                         !((uintptr_t)xbc & 15)) ? 1 : 0;
 #define CBIS_SCAN(NPL, LL)                                                                                          \
   return (int)launch_pdl(ssm_scan_kernel<TT, NPL, LL>, dim3((P + 256 / LL - 1) / (256 / LL), H, S), dim3(256), 0, st, \
                          (const TT*)xbc, xbc_ld, (const TT*)proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride, \
-                         seg_slot, cu_rows, y, y_ld, H, P, N, G)
+                         seg_slot, cu_rows, y, y_ld, H, P, N, G, use_async)
   if (L == 16) {
     if (N <= 64) CBIS_SCAN(4, 16);
     if (N <= 128) CBIS_SCAN(8, 16);

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_vekedra as pv
-from vekedra_helpers import (MIXED, ODD, assert_close, config, dense, latent, make_engine, make_weights, mamba, moe, plain,
+from vekedra_helpers import (MIXED, ODD, WIDE, assert_close, config, dense, latent, make_engine, make_weights, mamba, moe, plain,
                              run_cut, tokens_of, tolerance)
 
 pytestmark = pytest.mark.gpu
@@ -277,6 +277,34 @@ def test_whole_portions_and_token_by_token(name, dtype):
     for sizes in ([90], [2, 7, 2, 16, 3, 2, 9, 2, 25], [13, 1, 1, 1, 2], [1]):
         assert_close(run_cut(eng, toks, sizes), ref, dtype, cfgd, w, toks, sizes)
     assert eng.runner.graph_replays > 80
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wider_sizes_take_the_other_kernels(dtype):
+    """Eight layers whose sizes lead to the tensor-core, the tiled and the general attention kernels, long and short
+    windows over pages of 16, states of 64 and 128 (16 lanes a column for a single prompt): a prompt of 230 tokens
+    whole, in portions, and with its last 50 tokens decoded one by one; and two unequal requests in one batch."""
+    from cbis_b200.engine import StepEntry
+    cfgd = WIDE
+    w = make_weights(cfgd, 17)
+    toks = tokens_of(cfgd, 230, 5)
+    ref = plain(cfgd, w, toks)
+    eng = make_engine(cfgd, w, dtype, page_size=16, num_pages=40, max_batched_tokens=256)
+    for sizes in ([230], [100, 3, 64, 2, 61], [180] + [1] * 50):
+        assert_close(run_cut(eng, toks, sizes), ref, dtype, cfgd, w, toks, sizes)
+    other = tokens_of(cfgd, 75, 6)
+    a, b = eng.open_request(0), eng.open_request(1)
+    got_a, got_b = [], []
+    out = eng.forward_step([StepEntry(a, 0, toks[:120], list(range(120))), StepEntry(b, 0, other[:2], [0, 1])]).double().cpu()
+    got_a.append(out[:120]); got_b.append(out[120:])
+    out = eng.forward_step([StepEntry(b, 2, other[2:70], list(range(68))), StepEntry(a, 120, toks[120:121], [0])]).double().cpu()
+    got_b.append(out[:68]); got_a.append(out[68:])
+    for i in range(5):
+        out = eng.forward_step([StepEntry(a, 121 + i, toks[121 + i:122 + i], [0]),
+                                StepEntry(b, 70 + i, other[70 + i:71 + i], [0])]).double().cpu()
+        got_a.append(out[:1]); got_b.append(out[1:])
+    assert_close(torch.cat(got_a), ref[:126], dtype, cfgd, w, toks[:126], "a beside b")
+    assert_close(torch.cat(got_b), plain(cfgd, w, other), dtype, cfgd, w, other, "b beside a")
 
 
 def mixed_schedule(eng, cfgd, seqs, plan, order):

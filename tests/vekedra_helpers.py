@@ -49,6 +49,20 @@ ODD = config(48, 61, [
 ], scale=2.5, eps=1e-4)
 
 
+# sizes that take other kernels: latents of 64 and 128 (tensor-core attention), 96 (tiled), 192 and 256 (general), a
+# reader with another head count and window than the layer it reads, states of 64 and 128, four cache groups
+WIDE = config(128, 200, [
+    mamba(4, 32, 64, 2, 4, 2, mlp=moe(8, 2, 64)),
+    latent(4, 32, 48, 64, 70, 0.18, mlp=dense(192)),
+    latent(2, 64, 32, 192, 33, 0.12, mlp=None),
+    mamba(2, 64, 128, 1, 3, 1, mlp=dense(128)),
+    latent(8, 16, 16, 64, 128, 0.25, kv_from=1, mlp=moe(4, 1, 32)),
+    latent(3, 32, 32, 96, 20, 0.18, mlp=dense(96)),
+    latent(2, 32, 64, 256, 50, 0.18, mlp=None),
+    latent(2, 64, 64, 128, 40, 0.12, mlp=dense(64)),
+], scale=6.0)
+
+
 def make_weights(cfgd, seed, std=0.25, tweak=None):
     """Random tensors of the configuration, values exact in bfloat16 (both precisions and the plain implementation
     then see the same numbers); ``tweak(tensors)`` may change some before they are rounded."""
