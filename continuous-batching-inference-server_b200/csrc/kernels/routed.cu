@@ -152,10 +152,10 @@ routed_down_kernel(const TT* hid, const TT* __restrict__ down, const int* ids, c
   }
 }
 
-// ---- many rows (bfloat16): the (row, choice) pairs sorted by expert, an expert's pairs in tiles of 64 rows, each tile's
+// ---- many rows (bfloat16): the (row, choice) pairs sorted by expert, an expert's pairs in tiles of 128 rows, each tile's
 // products on the tensor cores (mma.sync m16n8k16, 32-bit sums).  A pair's result depends on its own row alone: its
 // place in a tile changes no sum's order.
-constexpr int kTileM = 64, kTileN = 64, kTileK = 32, kLd = kTileK + 8;   // shared rows padded to 80 bytes
+constexpr int kTileM = 128, kTileN = 64, kTileK = 32, kLd = kTileK + 8;   // shared rows padded to 80 bytes
 
 // One block.  offsets [E + 1]; sorted [pairs]: the pairs expert by expert; per tile its expert, its first place in
 // `sorted` and its rows; n_tiles [1].
@@ -196,17 +196,25 @@ routed_plan_kernel(const int* ids, int n_pairs, int E, int* offsets, int* sorted
   }
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"((unsigned)__cvta_generic_to_shared(smem)));
+}
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// grid (max tiles, ceil(N / 64)), 128 threads: warp w owns rows 16 w .. 16 w + 15 of the tile and all 64 columns.
+// grid (max tiles, ceil(N / 64)), 256 threads: the eight warps own the eight 32 x 32 pieces of the 128 x 64 tile
+// (with 64 x 64 tiles the blocks drew 1.35 GB through L2 in 290 us at width 2,048: the L2's rate, not the tensor cores');
+// fragments come from shared memory by ldmatrix (rows 80 bytes apart: no two of a load's eight rows share a bank).
 // DUAL: A = h[pair / top] (K = width), B = the expert's gate rows and up rows; out = hid[pair] = act(s g) * (s u).
 // else: A = hid[pair] (K = inner), B = the expert's down matrix; y[pair] (or y[row] when top is 1) = sum (* weight).
 template <bool DUAL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 routed_tiles_kernel(const __nv_bfloat16* A, int a_ld, const __nv_bfloat16* __restrict__ Bw, const int* sorted,
                     const float* weights, const int* tile_expert, const int* tile_start, const int* tile_rows,
                     const int* n_tiles, void* out, int out_ld, int N, int K, int top, int act, int weight_on_input) {
@@ -223,94 +231,93 @@ routed_tiles_kernel(const __nv_bfloat16* A, int a_ld, const __nv_bfloat16* __res
   if (threadIdx.x < kTileM) pair_of[threadIdx.x] = threadIdx.x < rows ? sorted[start + threadIdx.x] : -1;
   __syncthreads();
   const __nv_bfloat16* B0 = Bw + (size_t)e * (DUAL ? 2 : 1) * N * K;      // [N (x2), K]
-  float acc[DUAL ? 2 : 1][8][4];
+  float acc[DUAL ? 2 : 1][2][4][4];      // [gate | up][16 rows of the warp's 32][8 columns of its 32][fragment]
 #pragma unroll
   for (int m = 0; m < (DUAL ? 2 : 1); ++m)
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[m][mt][j][i] = 0.f;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;      // warps 4 down, 2 across
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  // 64 rows x 32 columns = 256 pieces of 16 bytes per matrix, two per thread; the pieces of the NEXT 32 columns are
-  // fetched into registers while the tensor cores work on the ones in shared memory
+  // A: 128 rows x 32 columns = 512 pieces of 16 bytes, two per thread; B: 64 x 32 = 256 pieces per matrix, one per
+  // thread; the pieces of the NEXT 32 columns are fetched into registers while the tensor cores work on the ones in
+  // shared memory
   constexpr int NB = DUAL ? 2 : 1;
-  uint4 ra[2], rb[NB][2];
+  uint4 ra[2], rb[NB];
   const __nv_bfloat16* a_src[2];
-  const __nv_bfloat16* b_src[2];
-  int piece_k[2];
+  const int piece_k = (threadIdx.x & 3) * 8, piece_r = threadIdx.x >> 2;      // rows piece_r and piece_r + 64 of A
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
-    const int idx = threadIdx.x + it * 128, r = idx >> 2;
-    piece_k[it] = (idx & 3) * 8;
-    const int pair = pair_of[r];
+    const int pair = pair_of[piece_r + it * 64];
     a_src[it] = pair >= 0 ? A + (size_t)(DUAL ? pair / top : pair) * a_ld : nullptr;
-    b_src[it] = n0 + r < N ? B0 + (size_t)(n0 + r) * K : nullptr;
   }
+  const __nv_bfloat16* b_src = n0 + piece_r < N ? B0 + (size_t)(n0 + piece_r) * K : nullptr;
   auto fetch = [&](int k0) {
+    const int k = k0 + piece_k;
+    const bool k_ok = k < K;
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      const int k = k0 + piece_k[it];
-      const bool k_ok = k < K;
-      ra[it] = (a_src[it] && k_ok) ? *reinterpret_cast<const uint4*>(a_src[it] + k) : zero;
+    for (int it = 0; it < 2; ++it) ra[it] = (a_src[it] && k_ok) ? *reinterpret_cast<const uint4*>(a_src[it] + k) : zero;
 #pragma unroll
-      for (int m = 0; m < NB; ++m)
-        rb[m][it] = (b_src[it] && k_ok) ? *reinterpret_cast<const uint4*>(b_src[it] + (size_t)m * N * K + k) : zero;
-    }
+    for (int m = 0; m < NB; ++m)
+      rb[m] = (b_src && k_ok) ? *reinterpret_cast<const uint4*>(b_src + (size_t)m * N * K + k) : zero;
   };
   fetch(0);
   for (int k0 = 0; k0 < K; k0 += kTileK) {
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      const int r = (threadIdx.x + it * 128) >> 2;
-      *reinterpret_cast<uint4*>(&As[r][piece_k[it]]) = ra[it];
+    for (int it = 0; it < 2; ++it) *reinterpret_cast<uint4*>(&As[piece_r + it * 64][piece_k]) = ra[it];
 #pragma unroll
-      for (int m = 0; m < NB; ++m) *reinterpret_cast<uint4*>(&Bs[m][r][piece_k[it]]) = rb[m][it];
-    }
+    for (int m = 0; m < NB; ++m) *reinterpret_cast<uint4*>(&Bs[m][piece_r][piece_k]) = rb[m];
     if (k0 + kTileK < K) fetch(k0 + kTileK);
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < kTileK; kk += 16) {
-      uint32_t a[4];
-      const int ar = warp * 16 + (lane >> 2), ak = kk + (lane & 3) * 2;
-      a[0] = *reinterpret_cast<const uint32_t*>(&As[ar][ak]);
-      a[1] = *reinterpret_cast<const uint32_t*>(&As[ar + 8][ak]);
-      a[2] = *reinterpret_cast<const uint32_t*>(&As[ar][ak + 8]);
-      a[3] = *reinterpret_cast<const uint32_t*>(&As[ar + 8][ak + 8]);
+      uint32_t a[2][4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int bn = j * 8 + (lane >> 2);
+      for (int mt = 0; mt < 2; ++mt)      // rows (lane % 16), columns kk + 8 * (lane / 16): the four 8 x 8 quarters of A
+        ldmatrix_x4(a[mt], &As[wm + mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
-        for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
-          uint32_t b[2];
-          b[0] = *reinterpret_cast<const uint32_t*>(&Bs[m][bn][ak]);
-          b[1] = *reinterpret_cast<const uint32_t*>(&Bs[m][bn][ak + 8]);
-          mma_bf16(acc[m][j], a, b);
+      for (int m = 0; m < NB; ++m)
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {  // two blocks of 8 columns a load: (n, k), (n, k + 8), (n + 8, k), (n + 8, k + 8)
+          uint32_t b[4];
+          ldmatrix_x4(b, &Bs[m][wn + jp * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+          const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16(acc[m][mt][jp * 2], a[mt], b0);
+            mma_bf16(acc[m][mt][jp * 2 + 1], a[mt], b1);
+          }
         }
-      }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = warp * 16 + (lane >> 2) + half * 8;
-    const int pair = pair_of[r];
-    if (pair < 0) continue;
-    const float w = weights[pair];
+  for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm + mt * 16 + (lane >> 2) + half * 8;
+      const int pair = pair_of[r];
+      if (pair < 0) continue;
+      const float w = weights[pair];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int n = n0 + j * 8 + (lane & 3) * 2 + i;
-        if (n >= N) continue;
-        if (DUAL) {
-          const float s = weight_on_input ? w : 1.f;
-          from_f32(static_cast<__nv_bfloat16*>(out)[(size_t)pair * out_ld + n],
-                   activate(s * acc[0][j][half * 2 + i], act) * (s * acc[DUAL ? 1 : 0][j][half * 2 + i]));
-        } else {
-          static_cast<float*>(out)[(size_t)pair * out_ld + n] = weight_on_input ? acc[0][j][half * 2 + i] : w * acc[0][j][half * 2 + i];
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int n = n0 + wn + j * 8 + (lane & 3) * 2 + i;
+          if (n >= N) continue;
+          const float v0 = acc[0][mt][j][half * 2 + i];
+          if (DUAL) {
+            const float s = weight_on_input ? w : 1.f;
+            from_f32(static_cast<__nv_bfloat16*>(out)[(size_t)pair * out_ld + n],
+                     activate(s * v0, act) * (s * acc[DUAL ? 1 : 0][mt][j][half * 2 + i]));
+          } else {
+            static_cast<float*>(out)[(size_t)pair * out_ld + n] = weight_on_input ? v0 : w * v0;
+          }
         }
-      }
-  }
+    }
 }
 
 // out[row, n] (+)= y[row * top + 0, n] + y[row * top + 1, n] + ..., in that order; 32-bit.
@@ -365,12 +372,12 @@ CBIS_EXPORT int cbis_routed_tiles(const void* h, int h_ld, const void* gate_up, 
                                offsets, sorted, tile_expert, tile_start, tile_rows, n_tiles);
   if (err != cudaSuccess) return (int)err;
   typedef const __nv_bfloat16* bp;
-  err = launch_pdl(routed_tiles_kernel<true>, dim3(max_tiles, (F + kTileN - 1) / kTileN), dim3(128), 0, st, (bp)h, h_ld,
+  err = launch_pdl(routed_tiles_kernel<true>, dim3(max_tiles, (F + kTileN - 1) / kTileN), dim3(256), 0, st, (bp)h, h_ld,
                    (bp)gate_up, (const int*)sorted, weights, (const int*)tile_expert, (const int*)tile_start,
                    (const int*)tile_rows, (const int*)n_tiles, hid, F, F, W, top, act, weight_on_input);
   if (err != cudaSuccess) return (int)err;
   const bool direct = top == 1 && !accumulate;
-  err = launch_pdl(routed_tiles_kernel<false>, dim3(max_tiles, (W + kTileN - 1) / kTileN), dim3(128), 0, st, (bp)hid, F,
+  err = launch_pdl(routed_tiles_kernel<false>, dim3(max_tiles, (W + kTileN - 1) / kTileN), dim3(256), 0, st, (bp)hid, F,
                    (bp)down, (const int*)sorted, weights, (const int*)tile_expert, (const int*)tile_start,
                    (const int*)tile_rows, (const int*)n_tiles, (void*)(direct ? out : y), direct ? out_ld : W, W, F, top,
                    act, weight_on_input);

@@ -912,7 +912,7 @@ def _routed_plan_ints(pairs: int, experts: int) -> int:
 
 def routed_tiles(h, gate_up, down, ids, weights, act, weight_on_input, out, accumulate=False):
     """The routed feed-forward for many rows of bfloat16: the (row, choice) pairs are sorted by expert on the device, an
-    expert's pairs run in tiles of 64 rows on the tensor cores (gate and up with the gated activation in one kernel,
+    expert's pairs run in tiles of 128 rows on the tensor cores (gate and up with the gated activation in one kernel,
     then down), and a row's choices are summed in their order.  ``out`` 32-bit ``[rows, width]``, overwritten or, with
     ``accumulate``, added to.  Nothing is read back to the host: it can be captured."""
     _need_cuda(h, gate_up, down, ids, weights, out)
