@@ -9,6 +9,7 @@ that may differ between two models comes from ``config.json``; the tensor names 
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Any, Dict, Optional, Tuple
 
@@ -36,9 +37,12 @@ def _num(d, key, where, positive=True) -> float:
 
 
 def _only(d: Dict[str, Any], allowed, where: str) -> None:
+    """Keys the design does not have are reported and passed over: a folder may carry notes of its own."""
+    if not isinstance(d, dict):
+        raise ConfigError(f"config.json: {where.rstrip('.') or 'the top level'} must be an object, got {d!r}")
     extra = sorted(set(d) - set(allowed))
     if extra:
-        raise ConfigError(f"config.json: {where}unknown keys {extra}; known: {sorted(allowed)}")
+        warnings.warn(f"config.json: {where}unknown keys {extra} are ignored; known: {sorted(allowed)}", stacklevel=3)
 
 
 @dataclass(frozen=True)

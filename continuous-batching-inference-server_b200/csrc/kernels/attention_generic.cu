@@ -1,5 +1,5 @@
 // Paged key/value cache: writing a step's keys and values into pages, and a general
-// attention kernel over the pages (any head size up to 256, any page size, query heads
+// attention kernel over the pages (any head size up to 512, any page size, query heads
 // grouped over fewer key/value heads, optional window), in 32-bit arithmetic for both
 // storage types.  It is the whole attention of the 32-bit path and the fallback of the
 // bfloat16 path for head sizes the tensor-core kernels do not take.
@@ -210,13 +210,14 @@ static int launch_generic(const void* q, int q_ld, const void* kc, const void* v
   const int blocks = (int)((total + warps - 1) / warps);
   cudaError_t e;
 #define CBIS_LAUNCH(NPER)                                                                                            \
-  e = launch_pdl(paged_attention_generic_kernel<TT, NPER, (NPER <= 2 ? 16 : (NPER <= 4 ? 8 : 4))>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
+  e = launch_pdl(paged_attention_generic_kernel<TT, NPER, (NPER <= 2 ? 16 : (NPER <= 4 ? 8 : (NPER <= 8 ? 4 : 2)))>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
                  (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, out_ld, n_rows, \
                  n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial)
   if (hd <= 32) CBIS_LAUNCH(1);
   else if (hd <= 64) CBIS_LAUNCH(2);
   else if (hd <= 128) CBIS_LAUNCH(4);
-  else CBIS_LAUNCH(8);
+  else if (hd <= 256) CBIS_LAUNCH(8);
+  else CBIS_LAUNCH(16);
 #undef CBIS_LAUNCH
   if (e == cudaSuccess && n_chunks > 1)
     e = launch_pdl(prefill_merge_kernel<TT, false>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions, row_seq,
@@ -233,7 +234,7 @@ CBIS_EXPORT int cbis_paged_attention_generic(const void* q, int q_ld, const void
                                              int n_kv_head, int hd, int ps, float scale, int window, int dtype,
                                              int n_chunks, int chunk_keys, float* partial, void* stream) {
   if (n_rows <= 0) return CBIS_OK;
-  if (hd <= 0 || hd > 256 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head) return CBIS_ERR_BAD_SIZE;
+  if (hd <= 0 || hd > 512 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head) return CBIS_ERR_BAD_SIZE;
   if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || !partial || hd % 4 || out_ld % 4 || ((uintptr_t)partial & 15) ||
                                         ((uintptr_t)out & 15))))
     return CBIS_ERR_BAD_SIZE;

@@ -89,7 +89,7 @@ def _need_cuda(*ts):
 
 
 NORM_MAX_WIDTH = 200 * 1024 // 4 - 33     # the widest row add_layernorm takes (cbis_norm_max_width() says the same)
-ATTENTION_MAX_HEAD_DIM = 256             # the general attention kernel's limit; the tiled ones take less and say so
+ATTENTION_MAX_HEAD_DIM = 512             # the general attention kernel's limit; the tiled ones take less and say so
 
 
 def embed_pos_add(tokens, positions, wte, wpe, out, err, multiplier: float = 1.0):
@@ -497,7 +497,7 @@ def generic_key_chunks(rows: int, n_head: int, max_context: int, head_dim: int):
     heads alone give 16 warps to each of the 148 SMs, or the head size is no multiple of 4; else chunks of a power
     of two of keys, at least 256, that do."""
     want = -(-16 * 148 // max(1, rows * n_head))
-    if want <= 1 or max_context <= 256 or head_dim % 4 or not USE_KEY_CHUNKS:
+    if want <= 1 or max_context <= 256 or head_dim % 4 or head_dim > 256 or not USE_KEY_CHUNKS:
         return 1, 0
     chunk = 256
     while chunk * want < max_context:
@@ -513,8 +513,8 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions
     context below n * keys); ``partial`` then holds ``rows * n_head * n * (head_dim + 4)`` floats."""
     _need_cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, partial)
     T = q.shape[0]
-    if head_dim > 256:
-        raise KernelError(f"attention: head_dim={head_dim} is above the kernel's limit of 256")
+    if head_dim > ATTENTION_MAX_HEAD_DIM:
+        raise KernelError(f"attention: head_dim={head_dim} is above the kernel's limit of {ATTENTION_MAX_HEAD_DIM}")
     if n_head % n_kv_head:
         raise KernelError(f"attention: n_head={n_head} is not a multiple of n_kv_head={n_kv_head}")
     assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.dtype == torch.int32

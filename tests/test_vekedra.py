@@ -249,6 +249,11 @@ ALONE = {
     "mamba": config(32, 50, [mamba(2, 12, 10, 2, 3, 2, mlp=None)]),
     "dense": config(32, 50, [mamba(1, 8, 8, 1, 2, 1, mlp=dense(44))]),
     "routed": config(32, 50, [mamba(1, 8, 8, 1, 2, 1, mlp=moe(6, 2, 20))]),
+    # sizes that are multiples of nothing: no 16-byte load, no tensor-core tile fits
+    "ragged": config(36, 37, [latent(3, 10, 6, 20, 7, 0.3, mlp=moe(3, 2, 10)), mamba(3, 6, 5, 1, 4, 3, mlp=dense(22)),
+                              latent(1, 7, 9, 20, 5, 0.4, kv_from=0, mlp=None), mamba(1, 9, 3, 1, 3, 1, mlp=moe(2, 2, 7))]),
+    # a latent wider than the tiled kernels' and the decode kernel's heads
+    "wide_latent": config(64, 50, [latent(2, 16, 16, 320, 12, 0.25, mlp=None), latent(3, 8, 8, 264, 9, 0.3, mlp=dense(24))]),
 }
 
 

@@ -47,7 +47,6 @@ def test_declared_tensors():
 
 @pytest.mark.parametrize("change, message", [
     (lambda c: c.pop("vocab"), "'vocab' is missing"),
-    (lambda c: c.update(rope=1), "unknown keys"),
     (lambda c: c["layers"][0].update(type="conv"), "is not one of"),
     (lambda c: c["layers"][2]["mixer"].update(kv_from=1), "keeps no latent"),
     (lambda c: c["layers"][2]["mixer"].update(kv_from=2), "earlier layer"),
@@ -63,6 +62,15 @@ def test_bad_configurations_are_refused(change, message):
     change(c)
     with pytest.raises(cb.ConfigError, match=message):
         cb.config_from_dict(c)
+
+
+def test_unknown_keys_are_reported_and_passed_over():
+    import cbis_b200 as cb
+    c = copy.deepcopy(MIXED)
+    c["notes"] = "made on a Tuesday"
+    c["layers"][1]["mixer"]["comment"] = 1
+    with pytest.warns(UserWarning, match="unknown keys"):
+        assert cb.config_from_dict(c) == cb.config_from_dict(MIXED)
 
 
 def _weights(cfgd, seed):
