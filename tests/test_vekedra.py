@@ -464,3 +464,58 @@ def test_greedy_generation_through_the_scheduler(dtype):
     assert eng.scheduler.idle()
     again = eng.generate(prompts[:2], cb.SamplingParams(max_new_tokens=new))     # slots and pages used again
     assert again == outs[:2]
+
+
+# ---- trace replay through bin/trace_run -------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_of_a_model_folder(dtype, tmp_path):
+    """A Vekedra folder (config.json, model.safetensors) through ``bin/trace_run``: a request whole; one with its last
+    20 tokens one by one; one in portions down to two tokens; and four live requests in mixed steps through a pool
+    smaller than the requests together, so that pages and state slots are used again."""
+    import json
+    import os
+
+    import numpy as np
+
+    from cbis_b200.weights.safetensors_io import write_safetensors
+    from replay_helpers import Trace, read_logits, run_trace
+    cfgd = MIXED
+    w = make_weights(cfgd, 23)
+    folder = str(tmp_path / "model")
+    os.makedirs(folder)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfgd, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), {k: v.to(torch.bfloat16) for k, v in w.items()})
+    lens = {"whole": 70, "tail": 50, "cut": 61, "m0": 40, "m1": 33, "m2": 64, "m3": 9, "m4": 21}
+    seqs = {r: tokens_of(cfgd, n, 90 + i) for i, (r, n) in enumerate(lens.items())}
+    t = Trace()
+    t.step([("whole", seqs["whole"], range(70))], end=["whole"])
+    t.step([("tail", seqs["tail"][:30], range(30))])
+    for i in range(30, 50):
+        t.step([("tail", seqs["tail"][i:i + 1], [0])], end=["tail"] if i == 49 else [])
+    pos = 0
+    for n in [16, 7, 2, 5, 2, 9, 3, 2, 15]:
+        t.step([("cut", seqs["cut"][pos:pos + n], range(n))], end=["cut"] if pos + n == 61 else [])
+        pos += n
+    plan = {"m0": [30, 2, 1, 1, 6], "m1": [2, 20, 1, 10], "m2": [50, 1, 1, 12], "m3": [9], "m4": [3, 1, 17]}
+    waiting, live, at, fed = list(plan), [], {}, {}
+    while waiting or live:
+        while waiting and len(live) < 4:
+            r = waiting.pop(0)
+            live.append(r); at[r] = 0; fed[r] = 0
+        entries, ended = [], []
+        for r in list(live):
+            n = plan[r][at[r]]
+            entries.append((r, seqs[r][fed[r]:fed[r] + n], range(n)))
+            fed[r] += n; at[r] += 1
+            if at[r] == len(plan[r]):
+                ended.append(r); live.remove(r)
+        t.step(entries, end=ended)
+    bound = t.live_tokens_bound()
+    assert bound < sum(-(-n // 64) * 64 for n in lens.values())
+    out = str(tmp_path / "out")
+    run_trace(t, folder, dtype, out, max_tokens=bound, page_size=8, env={"CBIS_POISON_FREED_PAGES": "1"})
+    got = read_logits(t, out, cfgd["vocab"])
+    for r, toks in seqs.items():
+        rows = torch.from_numpy(np.stack([got[(r, p)][0] for p in range(len(toks))])).double()
+        assert_close(rows, plain(cfgd, w, toks), dtype, cfgd, w, toks, r)
