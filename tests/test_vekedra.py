@@ -462,8 +462,13 @@ def test_greedy_generation_through_the_scheduler(dtype):
             assert tok == int(logits.argmax()), (len(p), len(seq))
             seq.append(tok)
     assert eng.scheduler.idle()
-    again = eng.generate(prompts[:2], cb.SamplingParams(max_new_tokens=new))     # slots and pages used again
+    again = eng.generate(prompts[:2], cb.SamplingParams(max_new_tokens=new))     # slots, pages and states used again
     assert again == outs[:2]
+    # a fresh engine whose decode graphs are captured ahead of serving, with requests of the engine's own that leave
+    # their states and pages behind
+    warm = make_engine(cfgd, w, dtype, num_pages=24, max_num_seqs=3, max_batched_tokens=64, prefill_chunk=16)
+    assert warm.warm_up() > 0
+    assert warm.generate(prompts[:2], cb.SamplingParams(max_new_tokens=new)) == outs[:2]
 
 
 # ---- trace replay through bin/trace_run -------------------------------------------------------------------------
