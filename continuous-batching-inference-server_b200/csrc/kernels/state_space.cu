@@ -119,7 +119,8 @@ template <typename TT, int NPL, int L>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_off, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ Dskip, float* state, long long slot_stride,
-                const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H, int P, int N, int G, int use_async) {
+                const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H, int P, int N, int G, int use_async,
+                int mode, int n_chunks, int chunk_rows, float* chunk_state, float* chunk_logdecay) {
   constexpr int NP = L * NPL;                       // the state size rounded up
   constexpr int TC = kScanTokens;
   constexpr int CB = 256 / L;                       // columns a block
@@ -137,20 +138,35 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
   if (!kAsyncFits) use_async = 0;
   pdl_trigger();
   pdl_wait();
-  const int h = blockIdx.y, s = blockIdx.z;
-  const int row0 = cu_rows[s], n_rows = cu_rows[s + 1] - row0;
-  if (n_rows <= 0) return;
+  // mode 0: a segment's rows from and into the request's state.  A long segment may instead be cut into n_chunks
+  // pieces of chunk_rows rows that run side by side: mode 1 walks every piece but the last from a zero state and
+  // leaves its end state and the sum of its log-decays; scan_chain_kernel turns these into every piece's start state;
+  // mode 2 walks every piece from its start state, writes y, and the last piece leaves the request's state.
+  const int h = blockIdx.y, s = blockIdx.z / n_chunks, chunk = blockIdx.z % n_chunks;
+  const int seg_row0 = cu_rows[s], seg_rows = cu_rows[s + 1] - seg_row0;
+  const int first_row = mode == 0 ? 0 : chunk * chunk_rows;
+  if (first_row >= seg_rows) return;
+  const int n_rows = mode == 0 ? seg_rows : min(chunk_rows, seg_rows - first_row);
+  const bool last_piece = first_row + n_rows == seg_rows;
+  if (mode == 1 && last_piece) return;          // nobody comes after it
+  const int row0 = seg_row0 + first_row;
   const int nl = threadIdx.x % L, pl = threadIdx.x / L;
   const int p = blockIdx.x * CB + pl;
   const bool live = p < P;
   const int g = h / (H / G);
   const int x_col0 = h * P + blockIdx.x * CB;
   const int b_col = H * P + g * N, c_col = H * P + G * N + g * N;
-  float* sp = state + (long long)seg_slot[s] * slot_stride + ((size_t)h * P + (live ? p : 0)) * N;
+  float* request_state = state + (long long)seg_slot[s] * slot_stride + ((size_t)h * P + (live ? p : 0)) * N;
+  float* piece_state = mode == 0 ? nullptr
+                                 : chunk_state + ((size_t)(s * n_chunks + chunk) * H * P + (size_t)h * P + (live ? p : 0)) * N;
+  float* sp = mode == 2 ? piece_state : request_state;      // where the walk starts from (mode 1: from zero)
   float S[NPL];
   // a lane's states lie side by side: 16-byte loads and stores where the row of states allows them
-  const bool vec = NPL >= 4 && N == NP && !((uintptr_t)sp & 15);
-  if (vec) {
+  const bool vec = NPL >= 4 && N == NP && !(((uintptr_t)request_state | (uintptr_t)piece_state) & 15);
+  if (mode == 1) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) S[i] = 0.f;
+  } else if (vec) {
 #pragma unroll
     for (int i = 0; i < NPL; i += 4) {
       const float4 v = live ? *reinterpret_cast<const float4*>(sp + nl * NPL + i) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -171,6 +187,7 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
   // what this thread fetches of a chunk of rows: values of B | C, of x, and (the first TC threads) a step size
   constexpr int E16 = 16 / (int)sizeof(TT);         // elements of a 16-byte piece
   float r_bc[BC_PER_THREAD], r_x[X_PER_THREAD], r_dt = 0.f;
+  float log_decay = 0.f;      // the first TC threads: the sum of -exp(A_log) dt over their rows of this walk
   auto fetch = [&](int first) {
     const int tc = min(TC, n_rows - first);
     if (threadIdx.x < TC)
@@ -227,6 +244,7 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
     if (threadIdx.x < TC) {
       const float dt = softplus_f32(r_dt + bias);
       dts[threadIdx.x] = dt;
+      if (first + (int)threadIdx.x < n_rows) log_decay += neg_a * dt;
       // The decay is applied as S += (decay - 1) S with decay - 1 = expm1(-exp(A_log) dt): a decay close to 1 rounded
       // to a float just below 1 loses most of the digits of 1 - decay, the same way at every step when the step size
       // barely changes, and a state that is read a thousand tokens later would carry a thousand times that error.
@@ -271,9 +289,16 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
       }
 #pragma unroll
       for (int o = 1; o < L; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && nl == 0) y[(size_t)(row0 + first + t) * y_ld + h * P + p] = fmaf(dskip, xv, acc);
+      if (live && nl == 0 && mode != 1) y[(size_t)(row0 + first + t) * y_ld + h * P + p] = fmaf(dskip, xv, acc);
     }
   }
+  if (mode == 1 && blockIdx.x == 0 && threadIdx.x < 32) {      // the piece's whole decay, as its logarithm
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) log_decay += __shfl_xor_sync(0xffffffffu, log_decay, o);   // threads >= TC hold 0
+    if (threadIdx.x == 0) chunk_logdecay[(size_t)(s * n_chunks + chunk) * H + h] = log_decay;
+  }
+  if (mode == 2 && !last_piece) return;         // only the last piece's end is the request's state
+  sp = mode == 1 ? piece_state : request_state;
   if (live && vec) {
 #pragma unroll
     for (int i = 0; i < NPL; i += 4)
@@ -288,23 +313,48 @@ ssm_scan_kernel(const TT* xbc, int xbc_ld, const TT* proj, int proj_ld, int dt_o
   }
 }
 
+// grid (ceil(H * P * N / 256), S): element e of segment s's state.  buf[s][c][e] holds piece c's end state from zero
+// (pieces before the last) and takes piece c's START state: S_0 = the request's state, S_(c+1) = S_c + expm1(l_c) S_c + E_c
+// with l_c the piece's summed log-decay of the element's head.
+__global__ void scan_chain_kernel(float* buf, const float* logdecay, const float* state, long long slot_stride,
+                                  const int* seg_slot, const int* cu_rows, int n_chunks, int chunk_rows, int H, int PN) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.y;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (long long)H * PN) return;
+  const int rows = cu_rows[s + 1] - cu_rows[s];
+  const int pieces = (rows + chunk_rows - 1) / chunk_rows;
+  if (pieces <= 0) return;
+  const int h = (int)(e / PN);
+  float S = state[(long long)seg_slot[s] * slot_stride + e];
+  for (int c = 0; c < pieces; ++c) {
+    float* at = buf + ((size_t)(s * n_chunks + c) * H) * PN + e;
+    const float end = c + 1 < pieces ? *at : 0.f;
+    *at = S;
+    if (c + 1 < pieces) S = fmaf(expm1f(logdecay[(size_t)(s * n_chunks + c) * H + h]), S, S + end);
+  }
+}
+
 template <typename TT>
 static int launch_scan(const void* xbc, int xbc_ld, const void* proj, int proj_ld, int dt_off, const float* dt_bias,
                        const float* A_log, const float* D, float* state, long long slot_stride, const int* seg_slot,
-                       const int* cu_rows, float* y, int y_ld, int S, int H, int P, int N, int G, cudaStream_t st) {
+                       const int* cu_rows, float* y, int y_ld, int S, int H, int P, int N, int G, int mode, int n_chunks,
+                       int chunk_rows, float* chunk_state, float* chunk_logdecay, cudaStream_t st) {
   // lanes a column: 8, or 16 while the warps (segments x heads x columns x lanes / 32) would not give every SM its
   // sixteen.  Not 32: the blocks of one long prompt (every one walks the whole prompt) must all run at once, and 512
   // blocks of 33 KB of shared memory do not (measured: 32 lanes took twice as long as 8).
   int L = 8;
-  if ((long long)S * H * P * L / 32 < 148 * 16 && N >= 64) L = 16;
+  if ((long long)S * n_chunks * H * P * L / 32 < 148 * 16 && N >= 64) L = 16;
   // rows may come by cp.async where every run of B, C and x of a row starts on 16 bytes
   const int e16 = 16 / (int)sizeof(TT);
   const int use_async = (N % e16 == 0 && P % e16 == 0 && (H * P) % e16 == 0 && xbc_ld % e16 == 0 &&
                          !((uintptr_t)xbc & 15)) ? 1 : 0;
 #define CBIS_SCAN(NPL, LL)                                                                                          \
-  return (int)launch_pdl(ssm_scan_kernel<TT, NPL, LL>, dim3((P + 256 / LL - 1) / (256 / LL), H, S), dim3(256), 0, st, \
+  return (int)launch_pdl(ssm_scan_kernel<TT, NPL, LL>, dim3((P + 256 / LL - 1) / (256 / LL), H, S * n_chunks), dim3(256), 0, st, \
                          (const TT*)xbc, xbc_ld, (const TT*)proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride, \
-                         seg_slot, cu_rows, y, y_ld, H, P, N, G, use_async)
+                         seg_slot, cu_rows, y, y_ld, H, P, N, G, use_async, mode, n_chunks, chunk_rows, chunk_state, \
+                         chunk_logdecay)
   if (L == 16) {
     if (N <= 64) CBIS_SCAN(4, 16);
     if (N <= 128) CBIS_SCAN(8, 16);
@@ -370,16 +420,32 @@ CBIS_EXPORT int cbis_conv_state_update(const void* in, int in_ld, int c0, float*
 CBIS_EXPORT int cbis_ssm_scan(const void* xbc, int xbc_ld, const void* proj, int proj_ld, int dt_off,
                               const float* dt_bias, const float* A_log, const float* D, float* state,
                               long long slot_stride, const int* seg_slot, const int* cu_rows, float* y, int y_ld,
-                              int n_segments, int H, int P, int N, int G, int dtype, void* stream) {
+                              int n_segments, int H, int P, int N, int G, int dtype, int n_chunks, int chunk_rows,
+                              float* chunk_state, float* chunk_logdecay, void* stream) {
   if (n_segments <= 0) return CBIS_OK;
   if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G) return CBIS_ERR_BAD_SIZE;
-  if (n_segments > 65535 || H > 65535) return CBIS_ERR_TOO_LARGE;
+  if (n_chunks < 1 || (n_chunks > 1 && (chunk_rows < 1 || !chunk_state || !chunk_logdecay))) return CBIS_ERR_BAD_SIZE;
+  if ((long long)n_segments * n_chunks > 65535 || H > 65535) return CBIS_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == CBIS_F32)
-    return launch_scan<float>(xbc, xbc_ld, proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride, seg_slot,
-                              cu_rows, y, y_ld, n_segments, H, P, N, G, st);
-  if (dtype == CBIS_BF16)
-    return launch_scan<__nv_bfloat16>(xbc, xbc_ld, proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride,
-                                      seg_slot, cu_rows, y, y_ld, n_segments, H, P, N, G, st);
-  return CBIS_ERR_BAD_DTYPE;
+  auto run = [&](int mode) {
+    if (dtype == CBIS_F32)
+      return launch_scan<float>(xbc, xbc_ld, proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride, seg_slot,
+                                cu_rows, y, y_ld, n_segments, H, P, N, G, mode, n_chunks, chunk_rows, chunk_state,
+                                chunk_logdecay, st);
+    if (dtype == CBIS_BF16)
+      return launch_scan<__nv_bfloat16>(xbc, xbc_ld, proj, proj_ld, dt_off, dt_bias, A_log, D, state, slot_stride,
+                                        seg_slot, cu_rows, y, y_ld, n_segments, H, P, N, G, mode, n_chunks, chunk_rows,
+                                        chunk_state, chunk_logdecay, st);
+    return CBIS_ERR_BAD_DTYPE;
+  };
+  if (n_chunks == 1) return run(0);
+  // pieces side by side: end states from zero, the chain of start states, then every piece from its start state
+  int err = run(1);
+  if (err) return err;
+  const long long elems = (long long)H * P * N;
+  err = (int)launch_pdl(scan_chain_kernel, dim3((unsigned)((elems + 255) / 256), n_segments), dim3(256), 0, st, chunk_state,
+                        (const float*)chunk_logdecay, (const float*)state, slot_stride, seg_slot, cu_rows, n_chunks,
+                        chunk_rows, H, P * N);
+  if (err) return err;
+  return run(2);
 }

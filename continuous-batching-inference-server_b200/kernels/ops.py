@@ -828,23 +828,49 @@ def conv_state_update(x, c0, channels, taps, state, seg_slot, cu_rows, n_segment
     _check(st, "conv_state_update", f"channels={channels} taps={taps} segments={n_segments}")
 
 
+# A long segment of a state-space layer is cut into pieces that run side by side where the step's states are few:
+# measured on 2,048 rows (us, one piece -> pieces of 128 rows): 18 k state elements (segments x heads x columns x
+# states) 293 -> 81, 65 k 300 -> 147, 131 k 438 -> 252, 262 k 546 -> 476 or 473 -> 460, 524 k 578 -> 840: twice the
+# arithmetic pays only while one piece leaves most of the machine idle.
+SCAN_PIECE_ROWS = 128           # rows of a piece
+SCAN_PIECES_FROM = 384          # the longest segment of a step from which segments are cut
+SCAN_PIECES_MAX_STATE = 200_000  # state elements of a step up to which they are
+
+
 def ssm_scan(xbc, proj, dt_off, dt_bias, a_log, d_skip, state, seg_slot, cu_rows, n_segments, heads, head_dim, n_state,
-             groups, y):
+             groups, y, max_seg_rows=None, piece_rows=None):
     """The selective state-space recurrence over each segment's rows, from and into ``state`` ``[slots, >= heads *
     head_dim * n_state]`` (32-bit, laid out ``[head][column][state]``): per head, with dt = softplus(raw + dt_bias),
     S <- exp(-exp(a_log) dt) S + dt B x^T and y = S^T C + d_skip x.  ``xbc`` rows: x | B | C (compute type); the raw
-    step sizes are columns ``dt_off ..`` of ``proj``; ``y`` ``[T, heads * head_dim]`` 32-bit."""
+    step sizes are columns ``dt_off ..`` of ``proj``; ``y`` ``[T, heads * head_dim]`` 32-bit.
+
+    A segment's rows are walked in order.  Where the step's longest segment (``max_seg_rows``) is long and the step's
+    states are few, segments are cut into pieces of ``piece_rows`` rows that run side by side: every piece's end
+    state from zero, then the start states one after the other (S_next = S + expm1(sum of log-decays) S + end), then
+    every piece again from its start state.  That is twice the arithmetic for many times the parallel work; against
+    the walk in one piece the results differ by rounding only.  ``piece_rows`` names the size (0: never cut)."""
     _need_cuda(xbc, proj, dt_bias, a_log, d_skip, state, seg_slot, cu_rows, y)
     assert xbc.stride(1) == 1 and proj.stride(1) == 1 and y.dtype == torch.float32 and y.stride(1) == 1
     assert xbc.dtype == proj.dtype and state.dtype == torch.float32 and state.stride(1) == 1
     assert state.shape[1] >= heads * head_dim * n_state and xbc.shape[1] == heads * head_dim + 2 * groups * n_state
     assert all(t.dtype == torch.float32 and t.numel() == heads for t in (dt_bias, a_log, d_skip))
+    longest = int(max_seg_rows) if max_seg_rows is not None else 0
+    if piece_rows is None:
+        few = n_segments * heads * head_dim * n_state <= SCAN_PIECES_MAX_STATE
+        piece_rows = SCAN_PIECE_ROWS if (few and longest >= SCAN_PIECES_FROM) else 0
+    n_pieces = -(-longest // piece_rows) if piece_rows and longest > piece_rows else 1
+    ends = logs = None
+    if n_pieces > 1:
+        ends = torch.empty((n_segments * n_pieces, heads * head_dim * n_state), dtype=torch.float32, device=xbc.device)
+        logs = torch.empty((n_segments * n_pieces, heads), dtype=torch.float32, device=xbc.device)
     st = kernels().cbis_ssm_scan(_ptr(xbc), c_int(xbc.stride(0)), _ptr(proj), c_int(proj.stride(0)), c_int(dt_off),
                                  _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), ctypes.c_longlong(state.stride(0)),
                                  _ptr(seg_slot), _ptr(cu_rows), _ptr(y), c_int(y.stride(0)), c_int(n_segments),
                                  c_int(heads), c_int(head_dim), c_int(n_state), c_int(groups),
-                                 c_int(dtype_code(xbc.dtype)), _stream())
-    _check(st, "ssm_scan", f"heads={heads} head_dim={head_dim} state={n_state} groups={groups} segments={n_segments}")
+                                 c_int(dtype_code(xbc.dtype)), c_int(n_pieces), c_int(piece_rows or 0), _ptr(ends),
+                                 _ptr(logs), _stream())
+    _check(st, "ssm_scan", f"heads={heads} head_dim={head_dim} state={n_state} groups={groups} segments={n_segments} "
+                           f"pieces={n_pieces}", launches=3 if n_pieces > 1 else 1)
 
 
 ROUTE_SCORE = {"sigmoid": 0, "softmax": 1}

@@ -72,7 +72,8 @@ class StateSpaceMixer(Mixer):
         ops.conv_state_update(proj, inner, self.channels, self.taps, conv_state, ctx.seg_slot, ctx.cu_rows, ctx.n_segments)
         y = torch.empty((T, inner), dtype=torch.float32, device=h.device)
         ops.ssm_scan(xbc, proj, self.d_proj - self.heads, self.dt_bias, self.a_log, self.d_skip, ssm_state, ctx.seg_slot,
-                     ctx.cu_rows, ctx.n_segments, self.heads, self.head_dim, self.n_state, self.groups, y)
+                     ctx.cu_rows, ctx.n_segments, self.heads, self.head_dim, self.n_state, self.groups, y,
+                     max_seg_rows=ctx.max_seg_rows)
         g = torch.empty((T, inner), dtype=h.dtype, device=h.device)
         ops.rms_norm(y, self.norm_w, self.eps, g, parts=self.norm_groups, gate=proj[:, :inner], gate_act="silu")
         if ops.linear_residual(g, self.w_out, ctx.residual):        # the product adds into the residual stream itself

@@ -102,11 +102,14 @@ def test_causal_convolution_over_steps(dtype, taps):
         assert (torch.cat(got[i]) - ref).abs().max() < tol * max(1.0, ref.abs().max())
 
 
+@pytest.mark.parametrize("pieces", [0, 32])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H, P, N, G", [(2, 8, 16, 1), (4, 40, 12, 2), (3, 5, 100, 3), (2, 33, 200, 2)])
-def test_state_space_recurrence_over_steps(dtype, H, P, N, G):
+@pytest.mark.parametrize("H, P, N, G", [(2, 8, 16, 1), (4, 40, 12, 2), (3, 5, 100, 3), (2, 33, 200, 2), (2, 16, 128, 1)])
+def test_state_space_recurrence_over_steps(dtype, H, P, N, G, pieces):
     """Two requests whose rows come in unlike portions; one head decays by less than a thousandth a step, so what the
-    first tokens wrote is still most of the state at the end.  Against the recurrence in float64."""
+    first tokens wrote is still most of the state at the end.  Against the recurrence in float64.  ``pieces``: segments
+    walked in one piece, or cut into pieces of 32 rows that run side by side (seven of them, the last one short,
+    beside a segment of a single row)."""
     from cbis_b200.kernels import ops
     g = torch.Generator().manual_seed(H * 100 + N)
     inner, lens = H * P, (260, 31)
@@ -129,7 +132,8 @@ def test_state_space_recurrence_over_steps(dtype, H, P, N, G):
         ps = torch.cat([s[1][f:f + n] for s, f, n in zip(seqs, fed, portions)])
         seg_slot, cu = step_tables(portions, slots)
         y = torch.empty(xs.shape[0], inner, dtype=torch.float32, device="cuda")
-        ops.ssm_scan(xs, ps, 3, dt_bias.cuda(), a_log.cuda(), d_skip.cuda(), state, seg_slot, cu, 2, H, P, N, G, y)
+        ops.ssm_scan(xs, ps, 3, dt_bias.cuda(), a_log.cuda(), d_skip.cuda(), state, seg_slot, cu, 2, H, P, N, G, y,
+                     max_seg_rows=max(portions), piece_rows=pieces)
         at = 0
         for i, n in enumerate(portions):
             got[i].append(y[at:at + n].double().cpu())
@@ -435,6 +439,31 @@ def test_far_tokens_held_by_the_state():
             else:
                 tol = tolerance(dtype, ref)
                 assert err.max() < 2 * tol and err.median() < tol / 4, (sizes, err.max().item(), err.median().item())
+
+
+def test_long_prompts_cut_into_pieces(monkeypatch):
+    """The engine cuts the recurrence of a long prompt into pieces that run side by side (here from 64 rows on, in
+    pieces of 48, so that a 300-token prompt is seven pieces): whole, in portions and beside a second request, the
+    logits are the plain implementation's, and what the last piece leaves is the state decoding goes on from."""
+    from cbis_b200.engine import StepEntry
+    from cbis_b200.kernels import ops
+    monkeypatch.setattr(ops, "SCAN_PIECES_FROM", 64)
+    monkeypatch.setattr(ops, "SCAN_PIECE_ROWS", 48)
+    cfgd = config(32, 40, [mamba(2, 8, 16, 1, 4, 1, mlp=None), mamba(4, 4, 64, 2, 2, 2, mlp=dense(24))], scale=3.0)
+    w = make_weights(cfgd, 8)
+    toks, other = tokens_of(cfgd, 300, 4), tokens_of(cfgd, 131, 5)
+    ref, ref_other = plain(cfgd, w, toks), plain(cfgd, w, other)
+    for dtype in ("float32", "bfloat16"):
+        eng = make_engine(cfgd, w, dtype, num_pages=64, max_batched_tokens=512)
+        for sizes in ([300], [97, 2, 150, 51], [280] + [1] * 20):
+            assert_close(run_cut(eng, toks, sizes), ref, dtype, what=sizes)
+        a, b = eng.open_request(0), eng.open_request(1)
+        out = eng.forward_step([StepEntry(a, 0, toks[:200], list(range(200))), StepEntry(b, 0, other[:1], [0])]).double().cpu()
+        got_a, got_b = [out[:200]], [out[200:]]
+        out = eng.forward_step([StepEntry(b, 1, other[1:], list(range(130))), StepEntry(a, 200, toks[200:201], [0])]).double().cpu()
+        got_b.append(out[:130]); got_a.append(out[130:])
+        assert_close(torch.cat(got_a), ref[:201], dtype, what="a")
+        assert_close(torch.cat(got_b), ref_other, dtype, what="b")
 
 
 # ---- generation through the scheduler --------------------------------------------------------------------------
