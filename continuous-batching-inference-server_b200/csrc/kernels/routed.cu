@@ -11,9 +11,9 @@ namespace cbis {
 
 constexpr int kScoreSigmoid = 0, kScoreSoftmax = 1;
 
-// grid (rows), 128 threads; shared: E floats.  ids [rows, top] int32, weights [rows, top] float.
+// grid (rows), 256 threads; shared: E floats.  ids [rows, top] int32, weights [rows, top] float.
 template <typename TT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 route_topk_kernel(const TT* h, int h_ld, const TT* __restrict__ router, int* ids, float* weights, int W, int E, int top,
                   int score, int renormalize) {
   extern __shared__ float z[];
@@ -21,10 +21,27 @@ route_topk_kernel(const TT* h, int h_ld, const TT* __restrict__ router, int* ids
   pdl_wait();
   const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const TT* hr = h + (size_t)r * h_ld;
-  for (int e = warp; e < E; e += 4) {
+  constexpr int V = 16 / (int)sizeof(TT);      // elements of a 16-byte load
+  const bool vec = W % V == 0 && !(((uintptr_t)hr | (uintptr_t)router) & 15);
+  for (int e = warp; e < E; e += 8) {
     const TT* wr = router + (size_t)e * W;
     float acc = 0.f;
-    for (int k = lane; k < W; k += 32) acc = fmaf(to_f32(hr[k]), to_f32(wr[k]), acc);
+    if (vec) {
+      float a2 = 0.f;                           // two chains of sums: the loads of a step do not wait for one another
+      for (int k = lane * V; k < W; k += 32 * V) {
+        TT a[V], b[V];
+        *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(hr + k);
+        *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(wr + k);
+#pragma unroll
+        for (int i = 0; i < V; i += 2) {
+          acc = fmaf(to_f32(a[i]), to_f32(b[i]), acc);
+          a2 = fmaf(to_f32(a[i + 1]), to_f32(b[i + 1]), a2);
+        }
+      }
+      acc += a2;
+    } else {
+      for (int k = lane; k < W; k += 32) acc = fmaf(to_f32(hr[k]), to_f32(wr[k]), acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) z[e] = acc;
   }
@@ -397,10 +414,10 @@ CBIS_EXPORT int cbis_route_topk(const void* h, int h_ld, const void* router, int
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem = (size_t)E * sizeof(float);
   if (dtype == CBIS_F32)
-    return (int)launch_pdl(route_topk_kernel<float>, dim3(rows), dim3(128), smem, st, (const float*)h, h_ld,
+    return (int)launch_pdl(route_topk_kernel<float>, dim3(rows), dim3(256), smem, st, (const float*)h, h_ld,
                            (const float*)router, ids, weights, W, E, top, score, renormalize);
   if (dtype == CBIS_BF16)
-    return (int)launch_pdl(route_topk_kernel<__nv_bfloat16>, dim3(rows), dim3(128), smem, st, (const __nv_bfloat16*)h, h_ld,
+    return (int)launch_pdl(route_topk_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, st, (const __nv_bfloat16*)h, h_ld,
                            (const __nv_bfloat16*)router, ids, weights, W, E, top, score, renormalize);
   return CBIS_ERR_BAD_DTYPE;
 }
