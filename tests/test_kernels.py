@@ -228,10 +228,10 @@ def test_kv_write_and_generic_attention(ops, dtype, n_head, n_kv_head, hd, ps, w
 
 
 def test_attention_refuses_sizes_it_does_not_take(ops):
-    z = torch.zeros(1, 600, device="cuda")
+    z = torch.zeros(1, 1200, device="cuda")
     i = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
-    with pytest.raises(ops.KernelError, match="head_dim=300"):
-        ops.paged_attention_generic(z, z, z, i, i[0], i[0], z, 2, 2, 300, 16, 1.0)
+    with pytest.raises(ops.KernelError, match="head_dim=600"):      # refused before anything is launched
+        ops.paged_attention_generic(z, z, z, i, i[0], i[0], z, 2, 2, 600, 16, 1.0)
     with pytest.raises(ops.KernelError, match="not a multiple"):
         ops.paged_attention_generic(z, z, z, i, i[0], i[0], z, 3, 2, 32, 16, 1.0)
 
