@@ -21,8 +21,8 @@ constexpr int kConvRows = 32;      // rows of a segment that one block of the co
 template <typename TT>
 __global__ void __launch_bounds__(128)
 causal_conv_act_kernel(const TT* in, int in_ld, int c0, const float* __restrict__ w, const float* __restrict__ bias,
-                       const float* state, long long slot_stride, const int* seg_slot, const int* cu_rows, TT* out,
-                       int out_ld, int C, int K, int act) {
+                       float* state, long long slot_stride, const int* seg_slot, const int* cu_rows, TT* out,
+                       int out_ld, int C, int K, int act, int update_state) {
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.x * 128 + threadIdx.x;
@@ -31,7 +31,7 @@ causal_conv_act_kernel(const TT* in, int in_ld, int c0, const float* __restrict_
   const int first = blockIdx.z * kConvRows;
   if (c >= C || first >= n) return;
   const int last = min(n, first + kConvRows);
-  const float* st = state + (long long)seg_slot[s] * slot_stride;
+  float* st = state + (long long)seg_slot[s] * slot_stride;
   constexpr int M = kMaxTaps;
   float wk[M], hist[M - 1];
 #pragma unroll
@@ -66,6 +66,15 @@ causal_conv_act_kernel(const TT* in, int in_ld, int c0, const float* __restrict_
         for (int j = 0; j < M - 2; ++j) hist[j] = hist[j + 1];
         hist[M - 2] = cur[u];
       }
+    }
+  }
+  // `update_state` (only where no segment is longer than one block's rows, so this block has seen all of them and
+  // nobody else reads this channel's state): the window now ends with the segment's last row
+  if (update_state) {
+#pragma unroll
+    for (int j = 0; j < M - 1; ++j) {
+      const int place = j - (M - K);             // state place of window place j
+      if (place >= 0) st[(size_t)place * C + c] = hist[j];
     }
   }
 }
@@ -379,22 +388,28 @@ CBIS_EXPORT int cbis_scan_max_state() { return 256; }
 
 // in: [T, in_ld] of the compute type, the convolution's channels at columns c0 .. c0 + C - 1; out: [T, out_ld].
 // w [C, K] and bias [C] 32-bit; state: 32-bit, (K-1) * C floats at `state + slot * slot_stride`.
+CBIS_EXPORT int cbis_conv_rows_per_block() { return kConvRows; }
+
+// `update_state` (max_seg_rows <= cbis_conv_rows_per_block() only): the kernel also leaves the state as
+// cbis_conv_state_update would.
 CBIS_EXPORT int cbis_causal_conv_act(const void* in, int in_ld, int c0, const float* w, const float* bias,
-                                     const float* state, long long slot_stride, const int* seg_slot, const int* cu_rows,
+                                     float* state, long long slot_stride, const int* seg_slot, const int* cu_rows,
                                      void* out, int out_ld, int C, int K, int act, int n_segments, int max_seg_rows,
-                                     int dtype, void* stream) {
+                                     int update_state, int dtype, void* stream) {
   if (n_segments <= 0 || max_seg_rows <= 0) return CBIS_OK;
   if (C <= 0 || K < 1 || K > kMaxTaps) return CBIS_ERR_BAD_SIZE;
+  if (update_state && max_seg_rows > kConvRows) return CBIS_ERR_BAD_SIZE;
   if (n_segments > 65535) return CBIS_ERR_TOO_LARGE;
   const dim3 grid((C + 127) / 128, n_segments, (max_seg_rows + kConvRows - 1) / kConvRows);
   if (grid.z > 65535) return CBIS_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == CBIS_F32)
     return (int)launch_pdl(causal_conv_act_kernel<float>, grid, dim3(128), 0, st, (const float*)in, in_ld, c0, w, bias,
-                           state, slot_stride, seg_slot, cu_rows, (float*)out, out_ld, C, K, act);
+                           state, slot_stride, seg_slot, cu_rows, (float*)out, out_ld, C, K, act, update_state);
   if (dtype == CBIS_BF16)
     return (int)launch_pdl(causal_conv_act_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, (const __nv_bfloat16*)in, in_ld,
-                           c0, w, bias, state, slot_stride, seg_slot, cu_rows, (__nv_bfloat16*)out, out_ld, C, K, act);
+                           c0, w, bias, state, slot_stride, seg_slot, cu_rows, (__nv_bfloat16*)out, out_ld, C, K, act,
+                           update_state);
   return CBIS_ERR_BAD_DTYPE;
 }
 

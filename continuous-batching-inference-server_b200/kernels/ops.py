@@ -801,11 +801,20 @@ def scan_max_state() -> int:
     return _limits["state"]
 
 
-def causal_conv_act(x, c0, channels, weight, bias, state, seg_slot, cu_rows, n_segments, max_seg_rows, act, out):
+def conv_rows_per_block() -> int:
+    if "conv_rows" not in _limits:
+        _limits["conv_rows"] = int(kernels().cbis_conv_rows_per_block())
+    return _limits["conv_rows"]
+
+
+def causal_conv_act(x, c0, channels, weight, bias, state, seg_slot, cu_rows, n_segments, max_seg_rows, act, out,
+                    update_state=False):
     """Causal convolution per channel over each segment's rows, bias and activation: the channels are columns
     ``c0 .. c0 + channels - 1`` of x; ``weight`` ``[channels, taps]`` (the last tap meets the current row) and
     ``bias`` 32-bit; ``state`` ``[slots, >= (taps-1)*channels]`` 32-bit holds every request's last taps-1 inputs
-    (zeros at a sequence's start) and is NOT changed (``conv_state_update`` does that afterwards)."""
+    (zeros at a sequence's start) and is NOT changed (``conv_state_update`` does that afterwards), unless
+    ``update_state`` is set, which a step may do whose longest segment has at most ``conv_rows_per_block()`` rows (a
+    decode step): the same kernel then leaves the state as ``conv_state_update`` would."""
     _need_cuda(x, weight, bias, state, seg_slot, cu_rows, out)
     taps = weight.shape[1]
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (x.shape[0], channels) and out.dtype == x.dtype
@@ -814,7 +823,8 @@ def causal_conv_act(x, c0, channels, weight, bias, state, seg_slot, cu_rows, n_s
     st = kernels().cbis_causal_conv_act(_ptr(x), c_int(x.stride(0)), c_int(c0), _ptr(weight), _ptr(bias), _ptr(state),
                                         ctypes.c_longlong(state.stride(0)), _ptr(seg_slot), _ptr(cu_rows), _ptr(out),
                                         c_int(out.stride(0)), c_int(channels), c_int(taps), c_int(ACT[act]),
-                                        c_int(n_segments), c_int(max_seg_rows), c_int(dtype_code(x.dtype)), _stream())
+                                        c_int(n_segments), c_int(max_seg_rows), c_int(1 if update_state else 0),
+                                        c_int(dtype_code(x.dtype)), _stream())
     _check(st, "causal_conv_act", f"channels={channels} taps={taps} segments={n_segments}")
 
 

@@ -67,9 +67,12 @@ class StateSpaceMixer(Mixer):
         proj = ops.linear(h, self.w_in, None)                   # z | x B C | raw dt
         ssm_state, conv_state = state[:, :cut], state[:, cut:]
         xbc = torch.empty((T, self.channels), dtype=h.dtype, device=h.device)
+        short = ctx.max_seg_rows <= ops.conv_rows_per_block()      # (a decode step) the convolution leaves the state itself
         ops.causal_conv_act(proj, inner, self.channels, self.conv_w, self.conv_b, conv_state, ctx.seg_slot, ctx.cu_rows,
-                            ctx.n_segments, ctx.max_seg_rows, "silu", xbc)
-        ops.conv_state_update(proj, inner, self.channels, self.taps, conv_state, ctx.seg_slot, ctx.cu_rows, ctx.n_segments)
+                            ctx.n_segments, ctx.max_seg_rows, "silu", xbc, update_state=short and self.taps > 1)
+        if not short:
+            ops.conv_state_update(proj, inner, self.channels, self.taps, conv_state, ctx.seg_slot, ctx.cu_rows,
+                                  ctx.n_segments)
         y = torch.empty((T, inner), dtype=torch.float32, device=h.device)
         ops.ssm_scan(xbc, proj, self.d_proj - self.heads, self.dt_bias, self.a_log, self.d_skip, ssm_state, ctx.seg_slot,
                      ctx.cu_rows, ctx.n_segments, self.heads, self.head_dim, self.n_state, self.groups, y,
