@@ -39,6 +39,11 @@ class LayerSpec:
     norm_feed_forward: PartSpec
     cache_source: Optional[int] = None
     norm_prefixes: Tuple[str, str] = ("ln_1.", "ln_2.")   # tensor-name prefixes of the two norms, after `prefix`
+    # norms AFTER the mixer and after the feed-forward (an arrangement that normalises a part's result before it is
+    # added to the stream), and their tensor-name prefixes; None: the arrangement has none
+    post_norm_mixer: Optional[PartSpec] = None
+    post_norm_feed_forward: Optional[PartSpec] = None
+    post_norm_prefixes: Tuple[str, str] = ("post_1.", "post_2.")
 
 
 @dataclass(frozen=True)

@@ -6,6 +6,11 @@
 //
 // Cache of one layer: K and V each [num_pages][n_kv_head][page_size][head_dim]; the
 // reference keeps [page][page_size][head][head_dim] (kernels/attention.cu:14,80).
+// Keys and values may have different widths (hd, hd_v), the values may be the first hd_v entries of the keys'
+// rows (one cached array for both: vc == kc, v_row == hd), and three things may change the scores and the softmax:
+//   * a distance bias: slope[h] * (p - j) is taken off the scaled score of the key at j for the query at p;
+//   * a query temperature: the score of the query at p is also multiplied by 1 + coef * ln(floor((p + 1) / every) + 1);
+//   * a sink: exp(sink[h]) counts once in the softmax's denominator and has no value.
 #include "attention_merge.cuh"
 
 namespace cbis {
@@ -15,7 +20,7 @@ namespace cbis {
 template <typename TT>
 __global__ void kv_write_kernel(const TT* qkv, int ld, int k_off, int v_off, TT* kc,
                                 TT* vc, const int* slot_mapping, int n_kv_head,
-                                int hd, int ps) {
+                                int hd, int hd_v, int ps) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
@@ -24,19 +29,21 @@ __global__ void kv_write_kernel(const TT* qkv, int ld, int k_off, int v_off, TT*
   const int page = slot / ps, off = slot % ps;
   const TT* krow = qkv + (size_t)r * ld + k_off;
   const TT* vrow = qkv + (size_t)r * ld + v_off;
-  const int width = n_kv_head * hd;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+  for (int c = threadIdx.x; c < n_kv_head * hd; c += blockDim.x) {
     const int h = c / hd, i = c % hd;
-    const size_t dst = (((size_t)page * n_kv_head + h) * ps + off) * hd + i;
-    kc[dst] = krow[c];
-    vc[dst] = vrow[c];
+    kc[(((size_t)page * n_kv_head + h) * ps + off) * hd + i] = krow[c];
+  }
+  if (vc == kc) return;     // one array stands for both: its rows are written
+  for (int c = threadIdx.x; c < n_kv_head * hd_v; c += blockDim.x) {
+    const int h = c / hd_v, i = c % hd_v;
+    vc[(((size_t)page * n_kv_head + h) * ps + off) * hd_v + i] = vrow[c];
   }
 }
 
 // The same with 16-byte moves, for head sizes that are a multiple of 8 (bfloat16) or 4 (float).
 template <typename TT>
 __global__ void kv_write_vec_kernel(const TT* qkv, int ld, int k_off, int v_off, TT* kc, TT* vc,
-                                    const int* slot_mapping, int n_kv_head, int hd, int ps) {
+                                    const int* slot_mapping, int n_kv_head, int hd, int hd_v, int ps) {
   constexpr int E = 16 / sizeof(TT);  // elements per 16 bytes
   pdl_trigger();
   pdl_wait();
@@ -46,12 +53,16 @@ __global__ void kv_write_vec_kernel(const TT* qkv, int ld, int k_off, int v_off,
   const int page = slot / ps, off = slot % ps;
   const TT* krow = qkv + (size_t)r * ld + k_off;
   const TT* vrow = qkv + (size_t)r * ld + v_off;
-  const int chunks = n_kv_head * hd / E, per_head = hd / E;
-  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-    const int h = c / per_head, i = (c % per_head) * E;
-    const size_t dst = (((size_t)page * n_kv_head + h) * ps + off) * hd + i;
-    *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(krow + c * E);
-    *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(vrow + c * E);
+  for (int c = threadIdx.x; c < n_kv_head * hd / E; c += blockDim.x) {
+    const int h = c / (hd / E), i = (c % (hd / E)) * E;
+    *reinterpret_cast<uint4*>(kc + (((size_t)page * n_kv_head + h) * ps + off) * hd + i) =
+        *reinterpret_cast<const uint4*>(krow + c * E);
+  }
+  if (vc == kc) return;
+  for (int c = threadIdx.x; c < n_kv_head * hd_v / E; c += blockDim.x) {
+    const int h = c / (hd_v / E), i = (c % (hd_v / E)) * E;
+    *reinterpret_cast<uint4*>(vc + (((size_t)page * n_kv_head + h) * ps + off) * hd_v + i) =
+        *reinterpret_cast<const uint4*>(vrow + c * E);
   }
 }
 
@@ -67,7 +78,9 @@ __global__ void paged_attention_generic_kernel(
     const TT* q, int q_ld, const TT* kc, const TT* vc,
     const int* block_table, int max_blocks, const int* row_seq,
     const int* positions, TT* __restrict__ out, int out_ld, int n_rows, int n_head, int n_kv_head,
-    int hd, int ps, float scale, int window, int n_chunks, int chunk_keys, float* partial) {
+    int hd, int ps, float scale, int window, int n_chunks, int chunk_keys, float* partial,
+    int hd_v, int v_row, const float* __restrict__ slopes, const float* __restrict__ sinks, float temp_coef,
+    int temp_every) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -80,9 +93,11 @@ __global__ void paged_attention_generic_kernel(
   const int seq = row_seq[row];
   if (seq < 0) {  // a padding row of a fixed-size batch
     if (chunk == 0)
-      for (int dim = lane; dim < hd; dim += 32) from_f32(out[(size_t)row * out_ld + h * hd + dim], 0.f);
+      for (int dim = lane; dim < hd_v; dim += 32) from_f32(out[(size_t)row * out_ld + h * hd_v + dim], 0.f);
     return;
   }
+  if (temp_every > 0) scale *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+  const float slope = slopes ? slopes[h] : 0.f;
   const int* bt = block_table + (size_t)seq * max_blocks;
   int kend = pos + 1;
   int kstart = window > 0 ? max(0, kend - window) : 0;
@@ -111,9 +126,9 @@ __global__ void paged_attention_generic_kernel(
       vptr[u] = nullptr;
       if (j < kend) {
         const int page = bt[j / ps];
-        const size_t base = (((size_t)page * n_kv_head + hk) * ps + (j % ps)) * hd;
-        const TT* kp = kc + base;
-        vptr[u] = vc + base;
+        const size_t token = ((size_t)page * n_kv_head + hk) * ps + (j % ps);
+        const TT* kp = kc + token * hd;
+        vptr[u] = vc + token * v_row;
 #pragma unroll
         for (int i = 0; i < NPER; ++i) {
           const int dim = lane + 32 * i;
@@ -123,7 +138,8 @@ __global__ void paged_attention_generic_kernel(
       s[u] = part;
     }
 #pragma unroll
-    for (int u = 0; u < G; ++u) s[u] = (j0 + u < kend) ? warp_sum(s[u]) * scale : -INFINITY;
+    for (int u = 0; u < G; ++u)
+      s[u] = (j0 + u < kend) ? fmaf(warp_sum(s[u]), scale, -slope * (float)(pos - (j0 + u))) : -INFINITY;
     float m_new = m;
 #pragma unroll
     for (int u = 0; u < G; ++u) m_new = fmaxf(m_new, s[u]);
@@ -140,7 +156,7 @@ __global__ void paged_attention_generic_kernel(
     for (int i = 0; i < NPER; ++i) {
       const int dim = lane + 32 * i;
       float a = acc[i] * corr;
-      if (dim < hd) {
+      if (dim < hd_v) {
 #pragma unroll
         for (int u = 0; u < G; ++u)
           if (vptr[u]) a = fmaf(p[u], to_f32(vptr[u][dim]), a);
@@ -150,23 +166,27 @@ __global__ void paged_attention_generic_kernel(
     m = m_new;
   }
   if (n_chunks > 1) {
-    float* dst = partial + ((size_t)w * n_chunks + chunk) * (hd + 4);
+    float* dst = partial + ((size_t)w * n_chunks + chunk) * (hd_v + 4);
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
       const int dim = lane + 32 * i;
-      if (dim < hd) dst[dim] = acc[i];
+      if (dim < hd_v) dst[dim] = acc[i];
     }
     if (lane == 0) {
-      dst[hd] = m;
-      dst[hd + 1] = l;
+      dst[hd_v] = m;
+      dst[hd_v + 1] = l;
     }
     return;
   }
-  const float inv = 1.f / l;
+  float inv = 1.f / l;
+  if (sinks) {      // the sink joins the denominator only: with the larger of the two as the reference
+    const float sk = sinks[h], mm = fmaxf(m, sk), keep = expf(m - mm);
+    inv = keep / fmaf(l, keep, expf(sk - mm));
+  }
 #pragma unroll
   for (int i = 0; i < NPER; ++i) {
     const int dim = lane + 32 * i;
-    if (dim < hd) from_f32(out[(size_t)row * out_ld + h * hd + dim], acc[i] * inv);
+    if (dim < hd_v) from_f32(out[(size_t)row * out_ld + h * hd_v + dim], acc[i] * inv);
   }
 }
 
@@ -174,29 +194,31 @@ __global__ void paged_attention_generic_kernel(
 
 using namespace cbis;
 
+// hd_v: the values' width (0: the keys').  kc == vc: one array stands for both and takes the rows at k_off.
 CBIS_EXPORT int cbis_kv_write(const void* qkv, int ld, int k_off, int v_off, void* kc, void* vc,
                               const int* slot_mapping, int T, int n_kv_head, int hd, int ps, int dtype,
-                              void* stream) {
+                              void* stream, int hd_v) {
   if (T <= 0) return CBIS_OK;
+  if (hd_v <= 0) hd_v = hd;
   if (n_kv_head <= 0 || hd <= 0 || ps <= 0) return CBIS_ERR_BAD_SIZE;
   const int width = n_kv_head * hd;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   cudaStream_t st = (cudaStream_t)stream;
   const int esz = dtype == CBIS_F32 ? 4 : 2, per16 = 16 / esz;
-  const bool vec = hd % per16 == 0 && ld % per16 == 0 && k_off % per16 == 0 && v_off % per16 == 0 &&
+  const bool vec = hd % per16 == 0 && hd_v % per16 == 0 && ld % per16 == 0 && k_off % per16 == 0 && v_off % per16 == 0 &&
                    !(((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc) & 15);
   if (vec && dtype == CBIS_F32)
     return (int)launch_pdl(kv_write_vec_kernel<float>, dim3(T), dim3(128), 0, st, (const float*)qkv, ld, k_off, v_off,
-                           (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, ps);
+                           (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, hd_v, ps);
   if (vec && dtype == CBIS_BF16)
     return (int)launch_pdl(kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, st, (const __nv_bfloat16*)qkv, ld,
-                           k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping, n_kv_head, hd, ps);
+                           k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping, n_kv_head, hd, hd_v, ps);
   if (dtype == CBIS_F32)
     return (int)launch_pdl(kv_write_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)qkv, ld, k_off, v_off,
-                           (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, ps);
+                           (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, hd_v, ps);
   if (dtype == CBIS_BF16)
     return (int)launch_pdl(kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, st, (const __nv_bfloat16*)qkv, ld,
-                           k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping, n_kv_head, hd, ps);
+                           k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping, n_kv_head, hd, hd_v, ps);
   return CBIS_ERR_BAD_DTYPE;
 }
 
@@ -204,7 +226,8 @@ template <typename TT>
 static int launch_generic(const void* q, int q_ld, const void* kc, const void* vc, const int* block_table,
                           int max_blocks, const int* row_seq, const int* positions, void* out, int out_ld,
                           int n_rows, int n_head, int n_kv_head, int hd, int ps, float scale, int window,
-                          int n_chunks, int chunk_keys, float* partial, cudaStream_t st) {
+                          int n_chunks, int chunk_keys, float* partial, int hd_v, int v_row, const float* slopes,
+                          const float* sinks, float temp_coef, int temp_every, cudaStream_t st) {
   const int warps = 4;
   const long long total = (long long)n_rows * n_head * n_chunks;
   const int blocks = (int)((total + warps - 1) / warps);
@@ -212,16 +235,18 @@ static int launch_generic(const void* q, int q_ld, const void* kc, const void* v
 #define CBIS_LAUNCH(NPER)                                                                                            \
   e = launch_pdl(paged_attention_generic_kernel<TT, NPER, (NPER <= 2 ? 16 : (NPER <= 4 ? 8 : (NPER <= 8 ? 4 : 2)))>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
                  (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, out_ld, n_rows, \
-                 n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial)
-  if (hd <= 32) CBIS_LAUNCH(1);
-  else if (hd <= 64) CBIS_LAUNCH(2);
-  else if (hd <= 128) CBIS_LAUNCH(4);
-  else if (hd <= 256) CBIS_LAUNCH(8);
+                 n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, hd_v, v_row, slopes, sinks, \
+                 temp_coef, temp_every)
+  const int widest = hd > hd_v ? hd : hd_v;
+  if (widest <= 32) CBIS_LAUNCH(1);
+  else if (widest <= 64) CBIS_LAUNCH(2);
+  else if (widest <= 128) CBIS_LAUNCH(4);
+  else if (widest <= 256) CBIS_LAUNCH(8);
   else CBIS_LAUNCH(16);
 #undef CBIS_LAUNCH
   if (e == cudaSuccess && n_chunks > 1)
     e = launch_pdl(prefill_merge_kernel<TT, false>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions, row_seq,
-                   (TT*)out, out_ld, 0, n_head, hd, window, n_chunks, chunk_keys);
+                   (TT*)out, out_ld, 0, n_head, hd_v, window, n_chunks, chunk_keys, sinks);
   return (int)e;
 }
 
@@ -232,18 +257,24 @@ CBIS_EXPORT int cbis_paged_attention_generic(const void* q, int q_ld, const void
                                              const int* block_table, int max_blocks, const int* row_seq,
                                              const int* positions, void* out, int out_ld, int n_rows, int n_head,
                                              int n_kv_head, int hd, int ps, float scale, int window, int dtype,
-                                             int n_chunks, int chunk_keys, float* partial, void* stream) {
+                                             int n_chunks, int chunk_keys, float* partial, void* stream,
+                                             int hd_v, int v_row, const float* slopes, const float* sinks,
+                                             float temp_coef, int temp_every) {
   if (n_rows <= 0) return CBIS_OK;
+  if (hd_v <= 0) hd_v = hd, v_row = hd;      // values as wide as the keys, in an array of their own
+  if (hd_v > 512 || v_row < hd_v) return CBIS_ERR_BAD_SIZE;
   if (hd <= 0 || hd > 512 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head) return CBIS_ERR_BAD_SIZE;
-  if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || !partial || hd % 4 || out_ld % 4 || ((uintptr_t)partial & 15) ||
+  if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || !partial || hd_v % 4 || out_ld % 4 || ((uintptr_t)partial & 15) ||
                                         ((uintptr_t)out & 15))))
     return CBIS_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == CBIS_F32)
     return launch_generic<float>(q, q_ld, kc, vc, block_table, max_blocks, row_seq, positions, out, out_ld, n_rows,
-                                 n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, st);
+                                 n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, hd_v, v_row,
+                                 slopes, sinks, temp_coef, temp_every, st);
   if (dtype == CBIS_BF16)
     return launch_generic<__nv_bfloat16>(q, q_ld, kc, vc, block_table, max_blocks, row_seq, positions, out, out_ld,
-                                         n_rows, n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, st);
+                                         n_rows, n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, hd_v, v_row,
+                                 slopes, sinks, temp_coef, temp_every, st);
   return CBIS_ERR_BAD_DTYPE;
 }

@@ -14,10 +14,11 @@ namespace cbis {
 // grid: the rows row0 .. row0+gridDim.x-1 of the step; a thread takes 4 head dims of one head at a time.
 // row_seq (may be null): the request of every row, negative for padding rows.
 // BASE2: the maxima are in the base-2 domain (scores times log2 e), else natural.
+// sinks (may be null): per head a score (natural domain) that counts once in the denominator and has no value.
 template <typename TO, bool BASE2>
 __global__ void __launch_bounds__(128)
 prefill_merge_kernel(const float* partial, const int* positions, const int* row_seq, TO* out, int out_ld, int row0,
-                     int n_head, int hd, int window, int n_chunks, int chunk_keys) {
+                     int n_head, int hd, int window, int n_chunks, int chunk_keys, const float* __restrict__ sinks) {
   pdl_trigger();
   pdl_wait();
   const int row = row0 + blockIdx.x;
@@ -30,6 +31,8 @@ prefill_merge_kernel(const float* partial, const int* positions, const int* row_
     const float* src = partial + ((size_t)blockIdx.x * n_head + h) * n_chunks * (hd + 4);
     float mx = -INFINITY;
     for (int c = c_lo; c <= c_hi; ++c) mx = fmaxf(mx, src[(size_t)c * (hd + 4) + hd]);
+    const float sink = sinks ? (BASE2 ? sinks[h] * 1.4426950408889634f : sinks[h]) : -INFINITY;
+    mx = fmaxf(mx, sink);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float l = 0.f;
     for (int c = c_lo; c <= c_hi; ++c) {
@@ -42,6 +45,7 @@ prefill_merge_kernel(const float* partial, const int* positions, const int* row_
       acc.w = fmaf(w, o.w, acc.w);
       l = fmaf(w, s[hd + 1], l);
     }
+    if (sinks) l += BASE2 ? exp2f(sink - mx) : expf(sink - mx);
     const float inv = 1.f / l;
     TO* dst = out + (size_t)row * out_ld + h * hd + d;
     if constexpr (sizeof(TO) == 4) {

@@ -293,6 +293,6 @@ CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc,
 #undef CBIS_PF
   if (e == cudaSuccess && n_chunks > 1)
     e = launch_pdl(prefill_merge_kernel<__nv_bfloat16, true>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions,
-                   (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd, window, n_chunks, chunk_keys);
+                   (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd, window, n_chunks, chunk_keys, (const float*)nullptr);
   return (int)e;
 }

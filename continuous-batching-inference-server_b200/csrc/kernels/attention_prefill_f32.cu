@@ -224,6 +224,6 @@ CBIS_EXPORT int cbis_paged_prefill_f32(const float* q, int q_ld, const float* kc
 #undef CBIS_PF32
   if (e == cudaSuccess && n_chunks > 1)
     e = launch_pdl(prefill_merge_kernel<float, false>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions, (const int*)nullptr, out, out_ld, row0,
-                   n_head, hd, window, n_chunks, chunk_keys);
+                   n_head, hd, window, n_chunks, chunk_keys, (const float*)nullptr);
   return (int)e;
 }

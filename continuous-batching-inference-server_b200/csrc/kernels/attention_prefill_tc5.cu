@@ -597,7 +597,7 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
   if (e == cudaSuccess && n_chunks > 1)
     e = launch_pdl(prefill_merge_kernel<__nv_bfloat16, true>, dim3(n_rows), dim3(128), 0, (cudaStream_t)stream,
                    (const float*)partial, positions, (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd, window,
-                   n_chunks, chunk_keys);
+                   n_chunks, chunk_keys, (const float*)nullptr);
   return (int)e;
 }
 

@@ -1,6 +1,6 @@
 // Gates and unit norms, all in 32-bit arithmetic whatever the storage type:
 //   * rms_norm: rows divided by their root mean square in equal parts, times a weight; an optional gate
-//     (act(z), element by element) is applied BEFORE the norm;
+//     (act(z), element by element) is applied BEFORE the norm, or (gate_after) to the normalised, weighted values;
 //   * gate_mul: out = act(a) * b, the inside of a gated feed-forward (a = gate, b = up) and an output gate
 //     (a = the gate's projection, b = the values, act = sigmoid).
 #include "common.cuh"
@@ -9,10 +9,12 @@ namespace cbis {
 
 // grid (rows, parts); part g of row r covers columns g*pw .. g*pw + pw - 1.
 //   v = x[r, c] * (gate ? act(gate[r, c]) : 1);  out[r, c] = v / sqrt(mean_c(v^2) + eps) * (weight ? weight[c] : 1)
+// With gate_after the gate stays out of v:  out[r, c] = x / sqrt(mean_c(x^2) + eps) * weight[c] * act(gate[r, c]).
 // With `staged` the part's v wait in shared memory (pw floats) between the two passes; else they are read again.
 template <typename TI, typename TG, typename TO>
 __global__ void rms_norm_kernel(const TI* x, int x_ld, const TG* gate, int gate_ld, int gate_act,
-                                const float* __restrict__ weight, float eps, TO* out, int out_ld, int pw, int staged) {
+                                const float* __restrict__ weight, float eps, TO* out, int out_ld, int pw, int staged,
+                                int gate_after) {
   extern __shared__ float vs[];
   __shared__ float red[33];
   pdl_trigger();
@@ -23,7 +25,7 @@ __global__ void rms_norm_kernel(const TI* x, int x_ld, const TG* gate, int gate_
   float ss = 0.f;
   for (int c = threadIdx.x; c < pw; c += blockDim.x) {
     float v = to_f32(xr[c]);
-    if (gr) v *= activate(to_f32(gr[c]), gate_act);
+    if (gr && !gate_after) v *= activate(to_f32(gr[c]), gate_act);
     if (staged) vs[c] = v;
     ss += v * v;
   }
@@ -35,10 +37,11 @@ __global__ void rms_norm_kernel(const TI* x, int x_ld, const TG* gate, int gate_
       v = vs[c];
     } else {
       v = to_f32(xr[c]);
-      if (gr) v *= activate(to_f32(gr[c]), gate_act);
+      if (gr && !gate_after) v *= activate(to_f32(gr[c]), gate_act);
     }
     v *= inv;
     if (weight) v *= weight[c0 + c];
+    if (gr && gate_after) v *= activate(to_f32(gr[c]), gate_act);
     from_f32(orow[c], v);
   }
 }
@@ -59,12 +62,12 @@ __global__ void gate_mul_kernel(const TT* a, int a_ld, const TT* b, int b_ld, TT
 
 template <typename TI, typename TG, typename TO>
 static int launch_rms(const void* x, int x_ld, const void* gate, int gate_ld, int gate_act, const float* weight,
-                      float eps, void* out, int out_ld, int rows, int parts, int pw, cudaStream_t st) {
+                      float eps, void* out, int out_ld, int rows, int parts, int pw, int gate_after, cudaStream_t st) {
   const int threads = pw >= 2048 ? 512 : (pw >= 512 ? 256 : (pw >= 128 ? 128 : 64));
   const int staged = pw <= 10240 ? 1 : 0;         // 40 KB of shared memory at most
   return (int)launch_pdl(rms_norm_kernel<TI, TG, TO>, dim3(rows, parts), dim3(threads),
                          staged ? (size_t)pw * sizeof(float) : 0, st, (const TI*)x, x_ld, (const TG*)gate, gate_ld,
-                         gate_act, weight, eps, (TO*)out, out_ld, pw, staged);
+                         gate_act, weight, eps, (TO*)out, out_ld, pw, staged, gate_after);
 }
 
 }  // namespace cbis
@@ -74,13 +77,13 @@ using namespace cbis;
 // x: 32-bit or the compute type (x_dtype); gate (may be null) and out: the compute type (dtype).
 CBIS_EXPORT int cbis_rms_norm(const void* x, int x_ld, int x_dtype, const void* gate, int gate_ld, int gate_act,
                               const float* weight, float eps, void* out, int out_ld, int dtype, int rows, int parts,
-                              int part_width, void* stream) {
+                              int part_width, void* stream, int gate_after) {
   if (rows <= 0) return CBIS_OK;
   if (parts <= 0 || part_width <= 0) return CBIS_ERR_BAD_SIZE;
   if (parts > 65535) return CBIS_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
 #define CBIS_RMS(TI, TG) \
-  return launch_rms<TI, TG, TG>(x, x_ld, gate, gate_ld, gate_act, weight, eps, out, out_ld, rows, parts, part_width, st)
+  return launch_rms<TI, TG, TG>(x, x_ld, gate, gate_ld, gate_act, weight, eps, out, out_ld, rows, parts, part_width, gate_after, st)
   if (dtype == CBIS_F32 && x_dtype == CBIS_F32) CBIS_RMS(float, float);
   if (dtype == CBIS_BF16 && x_dtype == CBIS_F32) CBIS_RMS(float, __nv_bfloat16);
   if (dtype == CBIS_BF16 && x_dtype == CBIS_BF16) CBIS_RMS(__nv_bfloat16, __nv_bfloat16);

@@ -13,6 +13,11 @@ keep the same contract: the query at position p sees the keys of its own request
 * 32-bit, head size in steps of 16 up to 128, longer segments: the tiled 32-bit kernel (decoding rows: the general
   kernel);
 * everything else: the general kernel, after the cache-write kernel.
+
+A mixer may also name (attributes, all optional): ``v_head_dim`` (values of another width than the keys; with one
+cached array for keys and values the values are the first entries of its rows), ``slopes`` (a distance bias per
+head), ``sinks`` (a number per head in the softmax's denominator) and ``q_temp`` (a query temperature by position).
+``run_attention`` returns how many columns a head's result takes in ``out``.
 """
 from __future__ import annotations
 
@@ -43,7 +48,20 @@ def _general_chunks(ctx, mixer, rows, hd):
     return chunks, partial
 
 
-def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
+def _extended(ctx, mixer, qkv, cache, view, out, k_pages, v_pages, k_off, v_off, vd, slopes, sinks, q_temp) -> int:
+    """Attention with values of their own width, a distance bias, a sink or a query temperature: the cache-write
+    kernel, then the general kernel over all rows (both precisions, any sizes)."""
+    T, hd, ps = ctx.n_rows, mixer.head_dim, cache.page_size
+    if mixer.own_kv:
+        ops.kv_write(qkv, k_off, v_off, k_pages, v_pages, view.slot_mapping, mixer.n_kv_head, hd, ps, v_head_dim=vd)
+    chunks, partial = _general_chunks(ctx, mixer, T, vd)
+    ops.paged_attention_generic(qkv[:, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq, ctx.positions,
+                                out[:, :mixer.n_head * vd], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
+                                mixer.window, chunks, partial, v_head_dim=vd, slopes=slopes, sinks=sinks, q_temp=q_temp)
+    return vd
+
+
+def run_attention(ctx, mixer, qkv, cache, view, out) -> int:
     nd = ctx.n_decode
     T = ctx.n_rows
     hd, ps = mixer.head_dim, cache.page_size
@@ -53,6 +71,15 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
     k_pages, v_pages = cache.arrays[k_name], cache.arrays[v_name]
     k_off = mixer.d_q
     v_off = k_off if v_name == k_name else k_off + mixer.d_kv      # one array for both: one column block for both
+    vd = int(getattr(mixer, "v_head_dim", 0) or hd)
+    slopes, sinks, q_temp = (getattr(mixer, a, None) for a in ("slopes", "sinks", "q_temp"))
+    if vd != hd or slopes is not None or sinks is not None or q_temp is not None:
+        return _extended(ctx, mixer, qkv, cache, view, out, k_pages, v_pages, k_off, v_off, vd, slopes, sinks, q_temp)
+    _plain(ctx, mixer, qkv, cache, view, out, nd, T, hd, ps, k_pages, v_pages, k_off, v_off)
+    return hd
+
+
+def _plain(ctx, mixer, qkv, cache, view, out, nd, T, hd, ps, k_pages, v_pages, k_off, v_off) -> None:
     fast_decode = qkv.dtype == torch.bfloat16 and hd % 8 == 0 and hd <= 256 and nd > 0
     first_general = nd if fast_decode else 0
     if fast_decode:

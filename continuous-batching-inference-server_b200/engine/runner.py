@@ -87,7 +87,7 @@ class StepContext:
 
     def attention(self, mixer, qkv, cache, view, out):
         """Stores this step's keys/values of ``mixer`` (if it keeps its own) and attends over the pages."""
-        run_attention(self, mixer, qkv, cache, view, out)
+        return run_attention(self, mixer, qkv, cache, view, out)
 
     def decode_scratch(self, n_floats: int, n_counters: int):
         """(float scratch, zeroed int32 counters) for kernels that split work and merge it in the last block."""

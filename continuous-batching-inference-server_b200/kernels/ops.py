@@ -480,15 +480,16 @@ def _bias_bf16(bias):
     return b16
 
 
-def kv_write(qkv, k_off, v_off, k_cache, v_cache, slot_mapping, n_kv_head, head_dim, page_size):
-    """Rows of this step's K and V (columns k_off.. and v_off.. of qkv) go to their token slots."""
+def kv_write(qkv, k_off, v_off, k_cache, v_cache, slot_mapping, n_kv_head, head_dim, page_size, v_head_dim=0):
+    """Rows of this step's K and V (columns k_off.. and v_off.. of qkv) go to their token slots.  ``v_head_dim``: the
+    values' width where it is not the keys'; one array given for both takes the rows at k_off only."""
     _need_cuda(qkv, k_cache, v_cache, slot_mapping)
     T = qkv.shape[0]
     assert qkv.stride(1) == 1 and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
     assert slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] >= T
     st = kernels().cbis_kv_write(_ptr(qkv), c_int(qkv.stride(0)), c_int(k_off), c_int(v_off), _ptr(k_cache),
                                  _ptr(v_cache), _ptr(slot_mapping), c_int(T), c_int(n_kv_head), c_int(head_dim),
-                                 c_int(page_size), c_int(dtype_code(qkv.dtype)), _stream())
+                                 c_int(page_size), c_int(dtype_code(qkv.dtype)), _stream(), c_int(v_head_dim))
     _check(st, "kv_write", f"T={T} kv_heads={n_kv_head} head_dim={head_dim} page={page_size}")
 
 
@@ -507,10 +508,16 @@ def generic_key_chunks(rows: int, n_head: int, max_context: int, head_dim: int):
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions, out, n_head, n_kv_head,
-                            head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None):
+                            head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None, v_head_dim=0,
+                            slopes=None, sinks=None, q_temp=None):
     """Attention of every row over its request's pages: keys max(0,p-window+1)..p for the query at p.
     ``chunks`` = (n, keys) from ``generic_key_chunks`` cuts every row's keys n ways over as many warps (every
-    context below n * keys); ``partial`` then holds ``rows * n_head * n * (head_dim + 4)`` floats."""
+    context below n * keys); ``partial`` then holds ``rows * n_head * n * (head_dim + 4)`` floats.
+    ``v_head_dim``: the values' width where it differs from the keys' (``out`` is then ``n_head * v_head_dim`` wide);
+    the value pages may be the key pages themselves, whose rows' first entries are then the values.  ``slopes`` (32-bit,
+    per head): slope * (p - j) is taken off the score of the key at j.  ``sinks`` (32-bit, per head): exp(sink) joins
+    the softmax's denominator.  ``q_temp`` = (coef, every): the scores of the query at p are multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1)."""
     _need_cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, partial)
     T = q.shape[0]
     if head_dim > ATTENTION_MAX_HEAD_DIM:
@@ -520,15 +527,23 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions
     assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.dtype == torch.int32
     assert block_table.is_contiguous() and row_seq.dtype == torch.int32 and positions.dtype == torch.int32
     n_chunks, chunk_keys = chunks
+    vd = int(v_head_dim) or head_dim
+    v_row = v_cache.shape[-1]
+    if vd > v_row:
+        raise KernelError(f"attention: values of {vd} do not fit pages of rows of {v_row}")
+    for t in (slopes, sinks):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n_head and t.is_cuda)
     if n_chunks > 1:
-        assert partial.dtype == torch.float32 and partial.numel() >= T * n_head * n_chunks * (head_dim + 4)
-        if out.stride(0) % 4 or out.data_ptr() % 16:
+        assert partial.dtype == torch.float32 and partial.numel() >= T * n_head * n_chunks * (vd + 4)
+        if out.stride(0) % 4 or out.data_ptr() % 16 or vd % 4:
             n_chunks, chunk_keys = 1, 0
+    coef, every = q_temp if q_temp else (0.0, 0)
     st = kernels().cbis_paged_attention_generic(
         _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(row_seq), _ptr(positions), _ptr(out), c_int(out.stride(0)), c_int(T), c_int(n_head), c_int(n_kv_head),
         c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(dtype_code(q.dtype)),
-        c_int(n_chunks), c_int(chunk_keys), _ptr(partial), _stream())
+        c_int(n_chunks), c_int(chunk_keys), _ptr(partial), _stream(), c_int(vd), c_int(v_row), _ptr(slopes), _ptr(sinks),
+        c_float(coef), c_int(int(every)))
     _check(st, "paged_attention_generic", f"T={T} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size} "
                                           f"chunks={n_chunks}x{chunk_keys}")
 
@@ -738,30 +753,34 @@ def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_
     _check(st, "decode_layers", f"layers={n_layers} rows={M} width={d} heads={n_head}/{n_kv_head} head_dim={head_dim} inner={F}")
 
 
-def linear_heads(x, w_hnk, out):
+def linear_heads(x, w_hnk, out, x_head_stride: int = 0, out_head_stride: int = 0):
     """Per head h: out[:, h*N:(h+1)*N] = x[:, h*K:(h+1)*K] @ w_hnk[h]^T; ``w_hnk`` is ``[heads, N, K]``, x and out
-    are 2-D with unit column stride (views of wider buffers are fine).  32-bit: this package's FFMA product,
-    head by head; bfloat16: one strided batched product of the library."""
+    are 2-D with unit column stride (views of wider buffers are fine).  With ``x_head_stride`` / ``out_head_stride``
+    a head's columns start every so many columns instead of every K / N (a head's part of wider per-head rows).
+    32-bit: this package's FFMA product, head by head; bfloat16: one strided batched product of the library."""
     _need_cuda(x, w_hnk, out)
     H, N, K = w_hnk.shape
     T = x.shape[0]
-    assert x.shape[1] == H * K and out.shape == (T, H * N) and x.stride(1) == 1 and out.stride(1) == 1
+    xs, os_ = int(x_head_stride) or K, int(out_head_stride) or N
+    assert x.shape[1] >= (H - 1) * xs + K and out.shape[1] >= (H - 1) * os_ + N and out.shape[0] == T
+    assert x.stride(1) == 1 and out.stride(1) == 1
     assert w_hnk.is_contiguous() and x.dtype == w_hnk.dtype == out.dtype
     if T == 0:
         return
     if x.dtype == torch.float32:
         for h in range(H):
-            linear_f32(x[:, h * K:(h + 1) * K], w_hnk[h], None, None, out[:, h * N:(h + 1) * N], w_is_nk=True)
+            linear_f32(x[:, h * xs:h * xs + K], w_hnk[h], None, None, out[:, h * os_:h * os_ + N], w_is_nk=True)
         return
-    xv = x.as_strided((H, T, K), (K, x.stride(0), 1), x.storage_offset())
-    ov = out.as_strided((H, T, N), (N, out.stride(0), 1), out.storage_offset())
+    xv = x.as_strided((H, T, K), (xs, x.stride(0), 1), x.storage_offset())
+    ov = out.as_strided((H, T, N), (os_, out.stride(0), 1), out.storage_offset())
     torch.bmm(xv, w_hnk.transpose(1, 2), out=ov)
 
 
-def rms_norm(x, weight, eps, out, parts: int = 1, gate=None, gate_act="silu"):
+def rms_norm(x, weight, eps, out, parts: int = 1, gate=None, gate_act="silu", gate_after: bool = False):
     """out = v / sqrt(mean(v^2) + eps) * weight in ``parts`` equal parts of the row, each by its own mean, with
     v = x * act(gate) if a gate is given (the gate comes BEFORE the norm).  x: 32-bit or ``out``'s type; gate and out:
-    the compute type; views with unit column stride are fine.  Arithmetic in 32-bit."""
+    the compute type; views with unit column stride are fine.  Arithmetic in 32-bit.  With ``gate_after`` the gate
+    stays out of the norm: out = x / sqrt(mean(x^2) + eps) * weight * act(gate)."""
     _need_cuda(x, weight, out, gate)
     rows, n = x.shape
     assert n % parts == 0 and out.shape == x.shape and x.stride(1) == 1 and out.stride(1) == 1
@@ -770,7 +789,7 @@ def rms_norm(x, weight, eps, out, parts: int = 1, gate=None, gate_act="silu"):
     st = kernels().cbis_rms_norm(_ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(gate),
                                  c_int(gate.stride(0) if gate is not None else 0), c_int(ACT[gate_act]), _ptr(weight),
                                  c_float(eps), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(rows),
-                                 c_int(parts), c_int(n // parts), _stream())
+                                 c_int(parts), c_int(n // parts), _stream(), c_int(1 if gate_after else 0))
     _check(st, "rms_norm", f"rows={rows} width={n} parts={parts}")
 
 
@@ -784,6 +803,96 @@ def gate_mul(a, b, act, out):
     st = kernels().cbis_gate_mul(_ptr(a), c_int(a.stride(0)), _ptr(b), c_int(b.stride(0)), _ptr(out), c_int(out.stride(0)),
                                  c_int(ACT[act]), c_int(rows), c_int(n), c_int(dtype_code(a.dtype)), _stream())
     _check(st, "gate_mul", f"rows={rows} n={n}")
+
+
+RMS_RESIDUAL_MAX_WIDTH = (200 * 1024 // 4 - 64) // 2     # the widest row add_rmsnorm takes (cbis_rms_residual_max_width() says the same)
+MATRIX_MEMORY_MAX_DIM = 512                              # the widest key of the matrix memory (cbis_matrix_memory_max_dim())
+
+
+def add_rmsnorm(x, delta, delta_bias, post, weight, eps, offset, out, rows=None):
+    """One pass over the rows of the 32-bit residual stream ``x``: what a part left (``delta``, 32-bit or the compute
+    type, plus ``delta_bias`` per column) is, with ``post`` = (weight, eps, offset), first divided by its own root mean
+    square and multiplied by (offset + weight); it is added to x in place; and ``out`` takes x / sqrt(mean(x^2) + eps)
+    * (offset + weight) (``weight`` None: x itself; ``out`` None: nothing).  With ``rows`` (int32) only those rows
+    are produced and x is not changed."""
+    _need_cuda(x, delta, delta_bias, weight, out, rows)
+    d = x.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    n = rows.shape[0] if rows is not None else x.shape[0]
+    assert out is None or (out.is_contiguous() and out.shape == (n, d))
+    assert delta is None or (delta.shape == x.shape and delta.stride(1) == 1)
+    pw, peps, poff = post if post is not None else (None, 0.0, 0.0)
+    for t in (delta_bias, pw, weight):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == d and t.is_contiguous())
+    st = kernels().cbis_add_rmsnorm(_ptr(x), _ptr(delta), c_int(delta.stride(0) if delta is not None else 0),
+                                    c_int(dtype_code(delta.dtype) if delta is not None else 0), _ptr(delta_bias), _ptr(pw),
+                                    c_float(peps), c_float(poff), _ptr(weight), c_float(eps), c_float(offset), _ptr(out),
+                                    c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows), c_int(n), c_int(d),
+                                    _stream())
+    _check(st, "add_rmsnorm", f"rows={n} width={d}")
+
+
+def rope_rows(src, src_col0, src_head_stride, dst, dst_col0, dst_head_stride, positions, heads, width, dims, freqs):
+    """In every row and head, ``width`` entries from column ``col0 + head * head_stride`` of ``src`` go to the like
+    place of ``dst``; the first ``dims`` of them rotated in pairs (entry i with entry i + dims/2) by the angle
+    position * freqs[i] (32-bit), the rest as they are.  src and dst may be one buffer."""
+    _need_cuda(src, dst, positions, freqs)
+    rows = src.shape[0]
+    assert src.dtype == dst.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and dst.shape[0] == rows
+    assert positions.dtype == torch.int32 and positions.shape[0] >= rows
+    assert dims == 0 or (freqs.dtype == torch.float32 and freqs.numel() >= dims // 2 and freqs.is_contiguous())
+    assert src_col0 + (heads - 1) * src_head_stride + width <= src.shape[1]
+    assert dst_col0 + (heads - 1) * dst_head_stride + width <= dst.shape[1]
+    st = kernels().cbis_rope_rows(_ptr(src), c_int(src.stride(0)), c_int(src_col0), c_int(src_head_stride), _ptr(dst),
+                                  c_int(dst.stride(0)), c_int(dst_col0), c_int(dst_head_stride), _ptr(positions),
+                                  c_int(rows), c_int(heads), c_int(width), c_int(dims), _ptr(freqs),
+                                  c_int(dtype_code(src.dtype)), _stream())
+    _check(st, "rope_rows", f"rows={rows} heads={heads} width={width} dims={dims}")
+
+
+def head_gate_mul(x, gate, heads, out):
+    """out[r, h, :] = x[r, h, :] * sigmoid(gate[r, h]): one gate number per row and head (32-bit or x's type);
+    x and out ``[rows, heads * width]``, views with unit column stride are fine."""
+    _need_cuda(x, gate, out)
+    rows, n = x.shape
+    assert n % heads == 0 and out.shape == x.shape and x.dtype == out.dtype and gate.shape == (rows, heads)
+    assert x.stride(1) == 1 and out.stride(1) == 1 and gate.stride(1) == 1
+    st = kernels().cbis_head_gate_mul(_ptr(x), c_int(x.stride(0)), _ptr(gate), c_int(gate.stride(0)),
+                                      c_int(dtype_code(gate.dtype)), _ptr(out), c_int(out.stride(0)), c_int(rows),
+                                      c_int(heads), c_int(n // heads), c_int(dtype_code(x.dtype)), _stream())
+    _check(st, "head_gate_mul", f"rows={rows} heads={heads} width={n // heads}")
+
+
+def matrix_memory_state_floats(heads: int, dim: int, v_dim: int) -> int:
+    """Floats of one request's state of the matrix memory (the kernel's own layout)."""
+    fn = kernels().cbis_matrix_memory_state_floats
+    fn.restype = ctypes.c_longlong
+    n = int(fn(c_int(heads), c_int(dim), c_int(v_dim)))
+    if n < 0:
+        raise KernelError(f"matrix_memory: heads={heads} dim={dim} v_dim={v_dim} are sizes the kernel does not take")
+    return n
+
+
+def matrix_memory(qkv, q_off, k_off, v_off, gates, i_bias, f_bias, cap, q_scale, den_eps, state, seg_slot, cu_rows,
+                  n_segments, heads, dim, v_dim, y):
+    """The recurrence of a matrix memory with exponential gates over every segment's rows, from and into the requests'
+    states: per head m' = max(lf + m, li), S <- exp(lf + m - m') S + exp(li - m') k v^T, n likewise with k alone,
+    y = S^T q / (max(|n . q|, exp(-m')) + den_eps), with li = cap tanh((i + i_bias) / cap) and
+    lf = logsigmoid(cap tanh((f + f_bias) / cap)).  ``qkv``: the compute type, q | k | v at their column offsets
+    (q is multiplied by ``q_scale``); ``gates``: 32-bit ``[T, 2 * heads]``, raw input gates then raw forget gates;
+    ``y``: 32-bit ``[T, heads * v_dim]``; ``state``: 32-bit ``[slots, matrix_memory_state_floats]``."""
+    _need_cuda(qkv, gates, i_bias, f_bias, state, seg_slot, cu_rows, y)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and gates.dtype == torch.float32 and gates.stride(1) == 1 and gates.shape == (T, 2 * heads)
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (T, heads * v_dim)
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= matrix_memory_state_floats(heads, dim, v_dim)
+    assert i_bias.dtype == f_bias.dtype == torch.float32 and i_bias.numel() == f_bias.numel() == heads
+    st = kernels().cbis_matrix_memory(_ptr(qkv), c_int(qkv.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(gates),
+                                      c_int(gates.stride(0)), _ptr(i_bias), _ptr(f_bias), c_float(cap), c_float(q_scale),
+                                      c_float(den_eps), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(seg_slot),
+                                      _ptr(cu_rows), _ptr(y), c_int(y.stride(0)), c_int(n_segments), c_int(heads), c_int(dim),
+                                      c_int(v_dim), c_int(dtype_code(qkv.dtype)), _stream())
+    _check(st, "matrix_memory", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim}")
 
 
 _limits = {}

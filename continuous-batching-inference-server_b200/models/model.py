@@ -37,14 +37,23 @@ class Layer:
         self.feed_forward = make_feed_forward(spec.feed_forward)
         self.norm_mixer = make_norm(spec.norm_mixer)
         self.norm_feed_forward = make_norm(spec.norm_feed_forward)
+        self.post_norm_mixer = make_norm(spec.post_norm_mixer) if spec.post_norm_mixer is not None else None
+        self.post_norm_feed_forward = (make_norm(spec.post_norm_feed_forward)
+                                       if spec.post_norm_feed_forward is not None else None)
         self.block = make_block(spec.arrangement, self.mixer, self.feed_forward, self.norm_mixer,
-                                self.norm_feed_forward)
+                                self.norm_feed_forward, self.post_norm_mixer, self.post_norm_feed_forward)
         self.norm_names = tuple(spec.norm_prefixes)
+        self.post_norm_names = tuple(spec.post_norm_prefixes)
 
     def parts(self):
         p = self.spec.prefix
-        return [(p, self.mixer), (p, self.feed_forward), (p + self.norm_names[0], self.norm_mixer),
-                (p + self.norm_names[1], self.norm_feed_forward)]
+        out = [(p, self.mixer), (p, self.feed_forward), (p + self.norm_names[0], self.norm_mixer),
+               (p + self.norm_names[1], self.norm_feed_forward)]
+        if self.post_norm_mixer is not None:
+            out.append((p + self.post_norm_names[0], self.post_norm_mixer))
+        if self.post_norm_feed_forward is not None:
+            out.append((p + self.post_norm_names[1], self.post_norm_feed_forward))
+        return out
 
 
 class Model:

@@ -2,12 +2,15 @@ from .base import (AttentionLike, Block, CacheArray, CacheNeed, Delta, Embedding
                    PositionEncoding, StateNeed, make_block, make_embedding, make_feed_forward, make_head, make_mixer,
                    make_norm, make_position, register_block, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position)
-from . import (attention, blocks, dense, embedding, head, latent_attention, layernorm, positions,  # noqa: F401
-               routed, state_space)  # (importing them registers the built-in kinds)
+from . import (attention, blocks, dense, embedding, gated_attention, head, latent_attention, layernorm,  # noqa: F401
+               matrix_memory, positions, rmsnorm, routed, state_space)  # (importing them registers the built-in kinds)
 from .attention import PagedAttention
-from .blocks import ParallelBlock, PreNormBlock
+from .blocks import ParallelBlock, PreNormBlock, SandwichBlock
 from .dense import DenseFeedForward, GatedFeedForward, NoFeedForward
+from .gated_attention import GatedAttention
 from .latent_attention import LatentAttention
+from .matrix_memory import MatrixMemoryMixer
+from .rmsnorm import RMSNorm
 from .routed import RoutedFeedForward
 from .state_space import StateSpaceMixer
 from .embedding import TokenTable

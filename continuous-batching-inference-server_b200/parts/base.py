@@ -13,7 +13,8 @@ Values that flow between parts:
 * the residual stream ``x``: float32 ``[T, width]`` in both precisions;
 * a part's input ``h`` (a norm's output): ``[T, width]`` in the compute dtype;
 * a part's output: a ``Delta``, the tensor to be added to the residual stream, plus
-  an optional bias row that the next norm adds in the same pass.
+  an optional bias row that the next norm adds in the same pass, plus (in a block that normalises
+  a part's result before it is added) the norm that it has to pass first.
 """
 from __future__ import annotations
 
@@ -27,9 +28,13 @@ from ..weights.loader import TensorDecl
 
 @dataclass
 class Delta:
-    """What a mixer or feed-forward adds to the residual stream: value (+ bias per column)."""
+    """What a mixer or feed-forward adds to the residual stream: value (+ bias per column).  ``post``: a norm that
+    value + bias passes BEFORE it is added (set by a block with norms after its parts); the norm that adds the
+    delta applies it in the same pass if it can (``Norm.takes_post``), else it is applied on its own
+    (``settle_delta``)."""
     value: torch.Tensor
     bias: Optional[torch.Tensor] = None
+    post: Optional["Norm"] = None
 
 
 @dataclass(frozen=True)
@@ -161,6 +166,14 @@ class Norm(Part):
         compute dtype.  With ``rows`` (int32 indices) only those rows are produced and x is not changed."""
         raise NotImplementedError
 
+    def takes_post(self, post: "Norm") -> bool:
+        """Whether ``forward`` applies ``post`` (a delta's norm of its own) itself, in its one pass."""
+        return False
+
+    def apply(self, ctx, value: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """norm(value + bias) as 32-bit rows, without any residual stream (a delta's norm applied on its own)."""
+        raise NotImplementedError
+
     def as_layernorm(self):
         """(weight, bias, eps) if this norm is exactly a LayerNorm with those (a part that normalises inside its
         own kernel asks for them), else None."""
@@ -205,12 +218,22 @@ class Head(Part):
         raise NotImplementedError
 
 
-class Block:
-    """Arrangement of norms, mixer and feed-forward around the residual stream."""
+def settle_delta(ctx, norm: Norm, delta: Optional[Delta]) -> Optional[Delta]:
+    """What ``norm`` can add as it is: a delta whose own norm ``norm`` does not apply in its pass gets it here."""
+    if delta is None or delta.post is None or norm.takes_post(delta.post):
+        return delta
+    return Delta(delta.post.apply(ctx, delta.value, delta.bias))
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norm_mixer: Norm, norm_feed_forward: Norm):
+
+class Block:
+    """Arrangement of norms, mixer and feed-forward around the residual stream.  ``post_norm_*``: norms AFTER the
+    parts, for the arrangements that have them."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norm_mixer: Norm, norm_feed_forward: Norm,
+                 post_norm_mixer: Optional[Norm] = None, post_norm_feed_forward: Optional[Norm] = None):
         self.mixer, self.feed_forward = mixer, feed_forward
         self.norm_mixer, self.norm_feed_forward = norm_mixer, norm_feed_forward
+        self.post_norm_mixer, self.post_norm_feed_forward = post_norm_mixer, post_norm_feed_forward
 
     def forward(self, ctx, x: torch.Tensor, pending: Optional[Delta], cache, state) -> Optional[Delta]:
         """Runs the layer; ``pending`` is the previous layer's output not yet added to x.
@@ -298,7 +321,10 @@ def make_head(spec) -> Head:
     return _make(_HEADS, "head", spec)
 
 
-def make_block(kind: str, mixer, feed_forward, norm_mixer, norm_feed_forward) -> Block:
+def make_block(kind: str, mixer, feed_forward, norm_mixer, norm_feed_forward, post_norm_mixer=None,
+               post_norm_feed_forward=None) -> Block:
     if kind not in _BLOCKS:
         raise KeyError(f"unknown block arrangement {kind!r}; known: {sorted(_BLOCKS)}")
-    return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward)
+    if post_norm_mixer is None and post_norm_feed_forward is None:
+        return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward)
+    return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward, post_norm_mixer, post_norm_feed_forward)

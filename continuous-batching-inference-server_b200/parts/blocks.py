@@ -7,9 +7,16 @@ import torch
 
 from ..kernels import ops
 from .attention import PagedAttention
-from .base import Block, register_block
-from .dense import DenseFeedForward
+from .base import Block, Delta, register_block, settle_delta
+from .dense import DenseFeedForward, NoFeedForward
 from .layernorm import LayerNorm
+
+
+def _add_pending(ctx, x, d) -> None:
+    """x += what a layer left pending (through the delta's own norm first, if it names one)."""
+    if d.post is not None:
+        d = Delta(d.post.apply(ctx, d.value, d.bias))
+    ops.add_delta(x, d.value, d.bias)
 
 
 class PreNormBlock(Block):
@@ -28,7 +35,7 @@ class PreNormBlock(Block):
         # back what is to be added.
         if self.mixer.fuses_norm(ctx, self.norm_mixer):
             if pending is not None:
-                ops.add_delta(x, pending.value, pending.bias)
+                _add_pending(ctx, x, pending)
             self.mixer.forward_residual(ctx, x, self.norm_mixer, cache, state)
             d = None
         else:
@@ -87,7 +94,7 @@ class PreNormBlock(Block):
         if plan is False:
             return super().forward_run(ctx, blocks, x, pending, caches, states)
         if pending is not None:            # what the layer before left to be added
-            ops.add_delta(x, pending.value, pending.bias)
+            _add_pending(ctx, x, pending)
         try:
             plan.run(ctx, x)
         except ops.KernelError as err:
@@ -159,5 +166,29 @@ class ParallelBlock(Block):
         return d
 
 
+class SandwichBlock(Block):
+    """Norms before AND after each part: x += post_1(mixer(norm_1(x))); x += post_2(feed_forward(norm_2(x))).
+    A part's result is handed on with its own norm attached (``Delta.post``); the norm before the next part applies
+    it, adds the result to the stream and normalises the stream in one pass where it can (``Norm.takes_post``).  A
+    part's result never goes into the stream directly (it has to be normalised first), so ``ctx.residual`` stays
+    unset.  A layer without a feed-forward is its first half only."""
+
+    def _after(self, ctx, d, post):
+        if d is None or post is None:
+            return d
+        if d.post is not None:         # a part that already named a norm of its own: that one first
+            d = Delta(d.post.apply(ctx, d.value, d.bias))
+        return Delta(d.value, d.bias, post)
+
+    def forward(self, ctx, x, pending, cache, state):
+        h = self.norm_mixer.forward(ctx, x, pending)
+        d = self._after(ctx, self.mixer.forward(ctx, h, cache, state), self.post_norm_mixer)
+        if isinstance(self.feed_forward, NoFeedForward):
+            return d
+        h = self.norm_feed_forward.forward(ctx, x, d)
+        return self._after(ctx, self.feed_forward.forward(ctx, h), self.post_norm_feed_forward)
+
+
 register_block("pre_norm", PreNormBlock)
 register_block("parallel", ParallelBlock)
+register_block("sandwich", SandwichBlock)

@@ -58,37 +58,53 @@ register_feed_forward("dense", DenseFeedForward)
 class GatedFeedForward(FeedForward):
     """down(act(gate h) * (up h)): three matrices stored ``[out, in]``, no biases; the gate's and the up
     projection's rows form one matrix, so one product gives both, and the activation and the product of the two
-    halves are taken in 32-bit and rounded once.  ``names``: what follows the layer's prefix in the names of the gate,
-    up and down matrices."""
+    halves are taken in 32-bit and rounded once.  With ``biases`` each of the three has a bias (its matrix's name with
+    ``.b``), added to the 32-bit sums.  ``names``: what follows the layer's prefix in the names of the gate, up and
+    down matrices."""
 
-    def __init__(self, width: int, inner: int, activation: str = "silu", names=("mlp.gate", "mlp.up", "mlp.down")):
+    def __init__(self, width: int, inner: int, activation: str = "silu", names=("mlp.gate", "mlp.up", "mlp.down"),
+                 biases: bool = False):
         if activation not in ops.ACT or not activation:
             raise ValueError(f"activation {activation!r} is not one of {sorted(k for k in ops.ACT if k)}")
         self.width, self.inner, self.activation = int(width), int(inner), activation
         self.gate_name, self.up_name, self.down_name = names
-        self.w_gate_up = self.w_down = None
+        self.biases = bool(biases)
+        self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
 
     def tensors(self, prefix):
-        return [TensorDecl(prefix + self.gate_name, (self.inner, self.width)),
-                TensorDecl(prefix + self.up_name, (self.inner, self.width)),
-                TensorDecl(prefix + self.down_name, (self.width, self.inner))]
+        out = [TensorDecl(prefix + self.gate_name, (self.inner, self.width)),
+               TensorDecl(prefix + self.up_name, (self.inner, self.width)),
+               TensorDecl(prefix + self.down_name, (self.width, self.inner))]
+        if self.biases:
+            out += [TensorDecl(prefix + self.gate_name + ".b", (self.inner,), "vector"),
+                    TensorDecl(prefix + self.up_name + ".b", (self.inner,), "vector"),
+                    TensorDecl(prefix + self.down_name + ".b", (self.width,), "vector")]
+        return out
 
     def load(self, prefix, tensors, dtype, device):
         self.w_gate_up = torch.cat([self._matrix(tensors[prefix + self.gate_name], dtype, device),
                                     self._matrix(tensors[prefix + self.up_name], dtype, device)]).contiguous()
         self.w_down = self._matrix(tensors[prefix + self.down_name], dtype, device)
+        if self.biases:
+            self.b_gate_up = torch.cat([self._vector(tensors[prefix + self.gate_name + ".b"], device),
+                                        self._vector(tensors[prefix + self.up_name + ".b"], device)]).contiguous()
+            self.b_down = self._vector(tensors[prefix + self.down_name + ".b"], device)
 
     def streamed_weights(self):
         return [self.w_gate_up, self.w_down]
 
     def forward(self, ctx, h):
         F = self.inner
-        gu = ops.linear(h, self.w_gate_up, None)
+        gu = ops.linear(h, self.w_gate_up, self.b_gate_up)
         a = torch.empty((h.shape[0], F), dtype=h.dtype, device=h.device)
         ops.gate_mul(gu[:, :F], gu[:, F:], self.activation, a)
-        if ops.linear_residual(a, self.w_down, ctx.residual):       # the product adds into the residual stream itself
+        if self.b_down is None:
+            if ops.linear_residual(a, self.w_down, ctx.residual):   # the product adds into the residual stream itself
+                return None
+        elif ops.linear_add_takes(a, self.w_down, ctx.residual):
+            ops.linear_add(a, self.w_down, self.b_down, ctx.residual)
             return None
-        return Delta(ops.linear(a, self.w_down, None, None, out_dtype=torch.float32))
+        return Delta(ops.linear(a, self.w_down, None, None, out_dtype=torch.float32), self.b_down)
 
 
 class NoFeedForward(FeedForward):

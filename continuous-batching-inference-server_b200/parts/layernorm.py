@@ -7,7 +7,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Delta, Norm, register_norm
+from .base import Delta, Norm, register_norm, settle_delta
 
 
 class LayerNorm(Norm):
@@ -35,6 +35,7 @@ class LayerNorm(Norm):
 
     def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
         n = rows.shape[0] if rows is not None else x.shape[0]
+        delta = settle_delta(ctx, self, delta)
         out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)
         ops.add_layernorm(x, delta.value if delta else None, delta.bias if delta else None,
                           self.weight, self.bias, self.eps, out, rows)
@@ -52,6 +53,7 @@ class NoNorm(Norm):
 
     def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
         n = rows.shape[0] if rows is not None else x.shape[0]
+        delta = settle_delta(ctx, self, delta)
         out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)
         ops.add_layernorm(x, delta.value if delta else None, delta.bias if delta else None, None, None, 0.0, out, rows)
         return out

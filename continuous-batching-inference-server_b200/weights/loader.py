@@ -18,7 +18,7 @@ import torch
 from .safetensors_io import WeightsError, read_safetensors
 
 
-ROLES = ("matrix", "table", "vector", "norm_weight", "norm_bias")
+ROLES = ("matrix", "table", "vector", "norm_weight", "norm_bias", "norm_zero")
 
 
 @dataclass(frozen=True)
@@ -27,8 +27,9 @@ class TensorDecl:
 
     role "matrix" / "table": used by matrix products or row lookups, held in the
     compute dtype; "vector": a bias, "norm_weight" / "norm_bias": the scale and shift of
-    a norm; these three are always applied in 32-bit.  The role, never the name, tells
-    the random-weights mode how to draw a tensor (a norm's scale is drawn around 1).
+    a norm, "norm_zero": a norm's scale stored around zero (applied as 1 + w); these are always applied in
+    32-bit.  The role, never the name, tells the random-weights mode how to draw a tensor (a norm's scale is
+    drawn around 1, one stored around zero around 0).
     """
     name: str
     shape: Tuple[int, ...]

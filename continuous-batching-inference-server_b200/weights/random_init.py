@@ -36,7 +36,7 @@ def random_tensors(declared: Sequence[TensorDecl], seed: int, scheme: InitScheme
     program has to draw again (a plain implementation on the CPU) are drawn with ``draw_on="cpu"``."""
     draw_on = draw_on or device
     by_role = {"norm_weight": (1.0, scheme.norm_weight_std), "norm_bias": (0.0, scheme.norm_bias_std),
-               "vector": (0.0, scheme.bias_std), "matrix": (0.0, scheme.matrix_std),
+               "norm_zero": (0.0, scheme.norm_weight_std), "vector": (0.0, scheme.bias_std), "matrix": (0.0, scheme.matrix_std),
                "table": (0.0, scheme.matrix_std)}
     out = {}
     for d in declared:
