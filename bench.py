@@ -115,12 +115,13 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra"],
+    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra", "figotar"],
                     help="1.3b: the default measurement; 6.7b: batch-64 decode at context 2,048; "
                          "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each); "
                          "batching: the reference's own workload at the reference's own sizes (both --impl arms); "
                          "vekedra: prefill and decode of the Vekedra design at two layer sizes beside the GPT-2 style model "
-                         "of equal width and depth, and its own kernels one by one against their bytes")
+                         "of equal width and depth, and its own kernels one by one against their bytes; "
+                         "figotar: the same for the Figotar design, beside Vekedra and the GPT-2 style model")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
@@ -155,6 +156,8 @@ def main() -> int:
         return mixed_workload(args, cb, torch)
     if args.config == "vekedra":
         return vekedra_workload(args, cb, torch)
+    if args.config == "figotar":
+        return figotar_workload(args, cb, torch)
     if args.config == "6.7b":
         args.skip_points = True
         args.batch = args.batch or 64
@@ -443,6 +446,55 @@ def vekedra_sizes(width, layers):
             "vocab": 32000, "width": width}
 
 
+def measure_model(args, cb, torch, pk, cfgd, vocab, B, P, T, steps, warm, gen):
+    """One model: the median time of a T-token prompt in one step (five runs after three), and decode steps of batch B
+    from context 1,024 as one captured graph with the argmax on the device."""
+    from cbis_b200.engine import StepEntry
+    from cbis_b200.kernels import ops
+    eng = cb.Engine.from_random(cfgd, seed=1234, dtype="bfloat16", page_size=args.page_size, max_tokens=B * P,
+                                max_num_seqs=B, max_batched_tokens=T, prefill_chunk=T, max_model_len=P)
+    mgr = eng.pool.manager
+    toks = torch.randint(0, vocab, (B, T), generator=gen).tolist()
+    times = []
+    for it in range(3 + 5):
+        slot = eng.open_request(it)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.forward_step([StepEntry(slot, 0, toks[0], [T - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+        eng.close_request(slot)
+    prefill_ms = statistics.median(times)
+    slots = [eng.open_request(100 + i) for i in range(B)]
+    for i, s in enumerate(slots):
+        eng.forward_step([StepEntry(s, 0, toks[i][:1024], [])])
+        assert mgr.append(s, warm + steps + 2)
+    ops.reset_launch_count()
+    loop = eng.runner.decode_loop([StepEntry(s, 1024, [1], [0]) for s in slots])
+    launches = ops.launch_count() // 2
+    loop.run(warm)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    loop.run(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    weights = eng.model.weight_bytes()
+    del loop
+    for s in slots:
+        eng.close_request(s)
+    del eng
+    torch.cuda.empty_cache()
+    return {"prefill_tokens_per_s": round(T / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+            "decode_tokens_per_s": round(B / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
+            "decode_launches_per_step": launches, "weight_bytes": int(weights),
+            "decode_weight_stream_frac": round(weights / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+
+
 def vekedra_workload(args, cb, torch) -> int:
     """Prefill (one 2,048-token prompt in one step) and decode (batch 8 from context 1,024, the captured step with
     argmax on the device) of the Vekedra design at two layer sizes, each beside the GPT-2 style model of equal width
@@ -456,48 +508,7 @@ def vekedra_workload(args, cb, torch) -> int:
     gen = torch.Generator().manual_seed(0)
 
     def measure(cfgd, vocab):
-        eng = cb.Engine.from_random(cfgd, seed=1234, dtype="bfloat16", page_size=args.page_size, max_tokens=B * P,
-                                    max_num_seqs=B, max_batched_tokens=T, prefill_chunk=T, max_model_len=P)
-        mgr = eng.pool.manager
-        toks = torch.randint(0, vocab, (B, T), generator=gen).tolist()
-        times = []
-        for it in range(3 + 5):
-            slot = eng.open_request(it)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            eng.forward_step([StepEntry(slot, 0, toks[0], [T - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            if it >= 3:
-                times.append(e0.elapsed_time(e1))
-            eng.close_request(slot)
-        prefill_ms = statistics.median(times)
-        slots = [eng.open_request(100 + i) for i in range(B)]
-        for i, s in enumerate(slots):
-            eng.forward_step([StepEntry(s, 0, toks[i][:1024], [])])
-            assert mgr.append(s, warm + steps + 2)
-        ops.reset_launch_count()
-        loop = eng.runner.decode_loop([StepEntry(s, 1024, [1], [0]) for s in slots])
-        launches = ops.launch_count() // 2
-        loop.run(warm)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        loop.run(steps)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        weights = eng.model.weight_bytes()
-        del loop
-        for s in slots:
-            eng.close_request(s)
-        del eng
-        torch.cuda.empty_cache()
-        return {"prefill_tokens_per_s": round(T / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
-                "decode_tokens_per_s": round(B / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
-                "decode_launches_per_step": launches, "weight_bytes": int(weights),
-                "decode_weight_stream_frac": round(weights / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        return measure_model(args, cb, torch, pk, cfgd, vocab, B, P, T, steps, warm, gen)
 
     sampler = ClockSampler()
     sampler.start()
@@ -612,6 +623,181 @@ def vekedra_kernels(torch, ops, pk):
             flops = 2.0 * rows * top * 3 * F * W
             us = out[f"routed_feed_forward_{tag}"]["us"]
             out[f"routed_feed_forward_{tag}"]["frac_of_bf16_peak"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+    return out
+
+
+def figotar_sizes(width, layers):
+    """A Figotar configuration with layers of the sizes a model of this width would have: of every four layers one
+    windowed attention (grouped key/value heads, values as wide as keys), one attention over a cached latent with a
+    rotated key part, and two matrix memories; every layer with a gated feed-forward."""
+    big = width >= 2048
+    hd = 128 if big else 64
+    heads = width // hd
+    att = {"dim": hd, "heads": heads, "kv_heads": max(1, heads // 4), "mask": {"size": 1024 if big else 512},
+           "q_temp": {"coef": 0.1, "every": 512}, "scale": hd ** -0.5, "vdim": hd}
+    lat = {"dim": 64, "heads": 16, "kv_rank": 96, "q_rank": width // 4, "rot": {"base": 10000.0, "dims": 32},
+           "rot_dim": 32, "scale": 96 ** -0.5, "vdim": 64}
+    mem = {"dim": hd, "gate_cap": 15.0, "heads": heads // 2, "vdim": 2 * hd}
+    mlp = {"kind": "dense", "ff": 8 * width // 3 // 64 * 64}
+    out = []
+    for i in range(layers):
+        kind = ("attention", "mlstm", "latent_attention", "mlstm")[i % 4]
+        out.append({"type": kind, "mixer": dict({"attention": att, "latent_attention": lat, "mlstm": mem}[kind]), "mlp": dict(mlp)})
+    return {"architecture": "Figotar", "layers": out, "norm": {"eps": 1e-6}, "vocab": 32000, "width": width}
+
+
+def figotar_workload(args, cb, torch) -> int:
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 from context 1,024, the captured step with
+    argmax on the device) of the Figotar design at two layer sizes, each beside Vekedra (the closest model: unlike
+    layers, a recurrent state, attention over a latent) and the GPT-2 style model of equal width and depth; then the
+    design's own kernels alone, at the larger size, beside the like kernels of those models."""
+    from cbis_b200.kernels import ops
+    pk = peaks()
+    P, T, B = 2048, 2048, args.batch or 8
+    steps, warm = min(args.steps, 128), max(3, min(args.warmup, 8))
+    layers = args.layers or 8
+    gen = torch.Generator().manual_seed(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for width in (1024, 2048):
+        gpt = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=layers, n_embd=width, n_head=16,
+                   n_inner=4 * width, vocab_size=32000, n_positions=P, activation_function="gelu",
+                   layer_norm_epsilon=1e-5, tie_word_embeddings=False)
+        sizes[f"width_{width}"] = {name: measure_model(args, cb, torch, pk, cfgd, 32000, B, P, T, steps, warm, gen)
+                                   for name, cfgd in (("figotar", figotar_sizes(width, layers)),
+                                                      ("vekedra", vekedra_sizes(width, layers)), ("gpt2_style", gpt))}
+    clocks = sampler.stop()
+    line = {"metric": f"Figotar prefill and decode tokens/s beside Vekedra and the GPT-2 style model of equal width and "
+                      f"depth ({layers} layers, batch {B}, prompt {T})", "unit": "tokens/s", "n_gpus": 1, "impl": "b200",
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "higher_is_better": True,
+            "value": sizes["width_2048"]["figotar"]["decode_tokens_per_s"], "sizes": sizes,
+            "kernels": figotar_kernels(torch, ops, pk), "clocks": clocks, "peaks": pk}
+    print(json.dumps(line))
+    return 0
+
+
+def figotar_kernels(torch, ops, pk):
+    """Microseconds of the design's own kernels alone (each replayed from a CUDA graph over buffers that rotate) at the
+    layer sizes of width 2,048, with the bytes each has to move over its time as a fraction of the measured copy
+    bandwidth (attention over prompts: its arithmetic as a fraction of the measured bf16 peak), each beside the like
+    kernel of the closest model at equal sizes."""
+    bf = torch.bfloat16
+    out = {}
+
+    def timed(make, nbytes, name, flops=0.0, reps=20, copies=4):
+        fns = [make() for _ in range(copies)]
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / reps / copies * 1e3
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "frac_of_copy_bandwidth": round(nbytes / us / 1e3 / pk["hbm_gbs"], 4)}
+        if flops:
+            out[name]["frac_of_bf16_peak"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+
+    W, H, D, V = 2048, 8, 128, 256                 # the matrix memory of width 2,048: 8 heads of 128 x 256
+    sH, sP, sN, sG = 64, 64, 128, 8                # the state-space layer of that width: 64 heads of 64 x 128
+    for rows, segs, tag in ((2048, 1, "prefill_2048"), (8, 8, "decode_8")):
+        per = rows // segs
+        seg_slot = torch.arange(segs, dtype=torch.int32, device="cuda")
+        cu = torch.arange(0, rows + 1, per, dtype=torch.int32, device="cuda")
+
+        def memory():
+            qkv = (torch.randn(rows, 2 * H * D + 2 * H * V, device="cuda") * 0.5).to(bf)
+            gates = torch.randn(rows, 2 * H, device="cuda")
+            ib, fb = torch.zeros(H, device="cuda"), torch.full((H,), 3.0, device="cuda")
+            st = torch.zeros(segs, ops.matrix_memory_state_floats(H, D, V), device="cuda")
+            y = torch.empty(rows, H * V, device="cuda")
+            return lambda: ops.matrix_memory(qkv, 0, H * D, 2 * H * D, gates, ib, fb, 15.0, D ** -0.5, 1e-6, st, seg_slot, cu,
+                                             segs, H, D, V, y)
+        timed(memory, rows * ((2 * H * D + H * V) * 2 + H * V * 4) + 2 * segs * H * D * V * 4, f"matrix_memory_{tag}")
+
+        def scan():
+            inner, C = sH * sP, sH * sP + 2 * sG * sN
+            xbc = (torch.randn(rows, C, device="cuda") * 0.5).to(bf)
+            proj = torch.randn(rows, 2 * inner + 2 * sG * sN + sH, device="cuda").to(bf)
+            v = [torch.zeros(sH, device="cuda") for _ in range(3)]
+            st = torch.zeros(segs, inner * sN, device="cuda")
+            y = torch.empty(rows, inner, device="cuda")
+            return lambda: ops.ssm_scan(xbc, proj, proj.shape[1] - sH, v[0], v[1], v[2], st, seg_slot, cu, segs, sH, sP, sN, sG, y)
+        timed(scan, rows * ((sH * sP + 2 * sG * sN) * 2 + sH * sP * 4) + 2 * segs * sH * sP * sN * 4, f"closest_model_ssm_scan_{tag}")
+
+        def sandwich():
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            w, wb = torch.zeros(W, device="cuda"), torch.zeros(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_rmsnorm(x, d, None, (wb, 1e-6, 1.0), w, 1e-6, 1.0, o)
+        timed(sandwich, rows * W * (4 + 4 + 4 + 2), f"add_rmsnorm_{tag}")
+
+        def lnorm():
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            w, b = torch.ones(W, device="cuda"), torch.zeros(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_layernorm(x, d, None, w, b, 1e-5, o)
+        timed(lnorm, rows * W * (4 + 4 + 4 + 2), f"closest_model_add_layernorm_{tag}")
+
+        def gated_norm():
+            y = torch.randn(rows, H * V, device="cuda")
+            z = torch.randn(rows, H * V, device="cuda").to(bf)
+            w = torch.ones(H * V, device="cuda")
+            o = torch.empty(rows, H * V, dtype=bf, device="cuda")
+            return lambda: ops.rms_norm(y, w, 1e-6, o, parts=H, gate=z, gate_act="sigmoid", gate_after=True)
+        timed(gated_norm, rows * H * V * (4 + 2 + 2), f"head_norm_with_gate_{tag}")
+
+    # attention: 16 query heads over 4 key/value heads of 128, a window of 1,024, pages of 16
+    nh, nkv, hd, ps, ctx_len = 16, 4, 128, 16, 2048
+    pages = ctx_len // ps
+    bt1 = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages)
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)], device="cuda")
+    cu1 = torch.tensor([0, ctx_len], dtype=torch.int32, device="cuda")
+    zero1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    keys = sum(min(i + 1, 1024) for i in range(ctx_len))
+    for name, extra in (("attention_prefill_2048_bias_temperature", dict(v_head_dim=hd, slopes=slopes, q_temp=(0.1, 512))),
+                        ("closest_model_attention_prefill_2048_same_kernel_plain", {})):
+        def prefill():
+            q = torch.randn(ctx_len, nh * hd, device="cuda").to(bf)
+            k, v = (torch.randn(pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+            o = torch.empty(ctx_len, nh * hd, dtype=bf, device="cuda")
+            return lambda: ops.paged_prefill_bf16(q, k, v, bt1, cu1, zero1, o, 0, 1, ctx_len, nh, nkv, hd, ps, hd ** -0.5, 1024, **extra)
+        timed(prefill, ctx_len * (2 * nh + 2 * nkv) * hd * 2, name, flops=4.0 * keys * nh * hd)
+    B = 8
+    btB = torch.arange(B * pages, dtype=torch.int32, device="cuda").view(B, pages)
+    row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    pos = torch.full((B,), ctx_len - 1, dtype=torch.int32, device="cuda")
+    slot_map = (btB[:, -1] * ps + ps - 1).contiguous()
+
+    def decode_general():
+        q = torch.randn(B, nh * hd, device="cuda").to(bf)
+        k, v = (torch.randn(B * pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+        o = torch.empty(B, nh * hd, dtype=bf, device="cuda")
+        chunks = ops.generic_key_chunks(B, nh, ctx_len, hd)
+        part = torch.empty(B * nh * max(1, chunks[0]) * (hd + 4), device="cuda")
+        return lambda: ops.paged_attention_generic(q, k, v, btB, row_seq, pos, o, nh, nkv, hd, ps, hd ** -0.5, 1024, chunks, part,
+                                                   v_head_dim=hd, slopes=slopes, q_temp=(0.1, 512))
+    timed(decode_general, B * 1024 * 2 * nkv * hd * 2, "attention_decode_8_bias_temperature")
+
+    def decode_plain():
+        qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda").to(bf)
+        k, v = (torch.randn(B * pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+        o = torch.empty(B, nh * hd, dtype=bf, device="cuda")
+        ns = ops.decode_splits(B, nh, ctx_len)
+        scratch = torch.empty(max(1, ops.decode_scratch_floats(B, nh, hd, ns)), device="cuda")
+        counters = torch.zeros(B * nh, dtype=torch.int32, device="cuda")
+        return lambda: ops.paged_decode_bf16(qkv, nh * hd, (nh + nkv) * hd, k, v, btB, row_seq, pos, slot_map, o, scratch, counters,
+                                             nh, nkv, hd, ps, hd ** -0.5, 1024, ns)
+    timed(decode_plain, B * 1024 * 2 * nkv * hd * 2, "closest_model_attention_decode_8")
     return out
 
 

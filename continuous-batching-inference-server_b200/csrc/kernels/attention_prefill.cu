@@ -9,6 +9,11 @@
 // tiles in flight); Q*K^T and P*V run on the tensor cores (mma.sync m16n8k16, bf16 in, 32-bit
 // accumulate; ldmatrix from rows padded by 16 bytes), and the softmax is the online form with
 // running max and sum per row in 32-bit, P rounded to bf16 only as the operand of P*V.
+//
+// Keys and values may be narrower than the tile (hdk, hdv <= HD, multiples of 8: the tiles' columns beyond them are
+// zero), the values may be the first hdv entries of the keys' rows (v_row: elements between two tokens' values),
+// and the scores may carry a distance bias (slope[h] * (p - j) taken off), a query temperature by position and a
+// sink in the denominator, as in the general kernel.
 #include "attention_merge.cuh"
 #include <math.h>
 
@@ -60,7 +65,9 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3)
 paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                           const int* block_table, int max_blocks, const int* cu_rows, const int* seg_start,
                           __nv_bfloat16* out, int out_ld, int seg0, int n_head, int n_kv_head, int ps_shift,
-                          float scale_log2e, int window, int n_chunks, int chunk_keys, float* partial, int row0) {
+                          float scale_log2e, int window, int n_chunks, int chunk_keys, float* partial, int row0,
+                          int hdk, int hdv, int v_row, const float* __restrict__ slopes,
+                          const float* __restrict__ sinks, float temp_coef, int temp_every) {
   constexpr int PITCH = HD + 8;  // elements per shared-memory row: 16 bytes of padding keep ldmatrix conflict-free
   constexpr int KS = HD / 16;    // k-steps of Q*K^T
   constexpr int DT = HD / 8;     // 8-wide column tiles of the output
@@ -95,17 +102,25 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   const int p0 = pos0 + lr0, p1 = pos0 + lr1;
   uint32_t qf[KS][4];
   {
-    const __nv_bfloat16* q0 = q + (size_t)(r_begin + tile * PF_BM + lr0) * q_ld + h * HD;
-    const __nv_bfloat16* q1 = q + (size_t)(r_begin + tile * PF_BM + lr1) * q_ld + h * HD;
+    const __nv_bfloat16* q0 = q + (size_t)(r_begin + tile * PF_BM + lr0) * q_ld + h * hdk;
+    const __nv_bfloat16* q1 = q + (size_t)(r_begin + tile * PF_BM + lr1) * q_ld + h * hdk;
     const bool v0 = lr0 < rows_here, v1 = lr1 < rows_here;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
-      qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t) : 0u;
-      qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t) : 0u;
-      qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t) : 0u;
-      qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t) : 0u;
+      const bool lo = ks * 16 + 2 * t < hdk, hi = ks * 16 + 8 + 2 * t < hdk;     // hdk is even: a pair is in or out
+      qf[ks][0] = v0 && lo ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t) : 0u;
+      qf[ks][1] = v1 && lo ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t) : 0u;
+      qf[ks][2] = v0 && hi ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t) : 0u;
+      qf[ks][3] = v1 && hi ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t) : 0u;
     }
   }
+  // per row: the scale with the query's temperature; per head: the distance bias and the sink, in the base-2 domain
+  float sc0 = scale_log2e, sc1 = scale_log2e;
+  if (temp_every > 0) {
+    sc0 *= 1.0f + temp_coef * logf((float)((p0 + 1) / temp_every + 1));
+    sc1 *= 1.0f + temp_coef * logf((float)((p1 + 1) / temp_every + 1));
+  }
+  const float slope2 = slopes ? slopes[h] * 1.4426950408889634f : 0.f;
   float o[DT][4];
 #pragma unroll
   for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
@@ -120,13 +135,14 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
       const int r = idx / CHUNKS, c = idx % CHUNKS;
       const int j = kt * PF_BN + r;
       const bool valid = j < kend && j >= live_from;   // pages behind the window may have been given back
-      size_t src = 0;
+      size_t token = 0;
       if (valid) {
         const int page = bt[j >> ps_shift];
-        src = (((size_t)page * n_kv_head + hk) * ps + (j & (ps - 1))) * HD + c * 8;
+        token = ((size_t)page * n_kv_head + hk) * ps + (j & (ps - 1));
       }
-      cp_async16(dk + r * PITCH + c * 8, kc + src, valid);
-      cp_async16(dv + r * PITCH + c * 8, vc + src, valid);
+      const bool in_k = valid && c * 8 < hdk, in_v = valid && c * 8 < hdv;
+      cp_async16(dk + r * PITCH + c * 8, kc + (in_k ? token * hdk + c * 8 : 0), in_k);
+      cp_async16(dv + r * PITCH + c * 8, vc + (in_v ? token * v_row + c * 8 : 0), in_v);
     }
     cp_async_commit();
   };
@@ -170,7 +186,11 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = j0 + nt * 8 + 2 * t + e;
-        float a = s[nt][e] * scale_log2e, b2 = s[nt][2 + e] * scale_log2e;
+        float a = s[nt][e] * sc0, b2 = s[nt][2 + e] * sc1;
+        if (slopes) {
+          a = fmaf(-slope2, (float)(p0 - j), a);
+          b2 = fmaf(-slope2, (float)(p1 - j), b2);
+        }
         if (edge) {
           if (j > p0 || (window > 0 && j < p0 - window + 1)) a = -INFINITY;
           if (j > p1 || (window > 0 && j < p1 - window + 1)) b2 = -INFINITY;
@@ -226,22 +246,30 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   if (n_chunks > 1) {   // unnormalised sums, maximum (base-2 domain) and denominator for the merge kernel
-    float* d0 = partial + (((size_t)(r_begin + tile * PF_BM + lr0 - row0) * n_head + h) * n_chunks + chunk) * (HD + 4);
-    float* d1 = partial + (((size_t)(r_begin + tile * PF_BM + lr1 - row0) * n_head + h) * n_chunks + chunk) * (HD + 4);
+    float* d0 = partial + (((size_t)(r_begin + tile * PF_BM + lr0 - row0) * n_head + h) * n_chunks + chunk) * (hdv + 4);
+    float* d1 = partial + (((size_t)(r_begin + tile * PF_BM + lr1 - row0) * n_head + h) * n_chunks + chunk) * (hdv + 4);
 #pragma unroll
     for (int d = 0; d < DT; ++d) {
+      if (d * 8 >= hdv) break;
       if (lr0 < rows_here) *reinterpret_cast<float2*>(d0 + d * 8 + 2 * t) = make_float2(o[d][0], o[d][1]);
       if (lr1 < rows_here) *reinterpret_cast<float2*>(d1 + d * 8 + 2 * t) = make_float2(o[d][2], o[d][3]);
     }
-    if (t == 0 && lr0 < rows_here) *reinterpret_cast<float2*>(d0 + HD) = make_float2(m0, l0);
-    if (t == 0 && lr1 < rows_here) *reinterpret_cast<float2*>(d1 + HD) = make_float2(m1, l1);
+    if (t == 0 && lr0 < rows_here) *reinterpret_cast<float2*>(d0 + hdv) = make_float2(m0, l0);
+    if (t == 0 && lr1 < rows_here) *reinterpret_cast<float2*>(d1 + hdv) = make_float2(m1, l1);
     return;
   }
-  const float i0 = 1.f / l0, i1 = 1.f / l1;
-  __nv_bfloat16* o0 = out + (size_t)(r_begin + tile * PF_BM + lr0) * out_ld + h * HD;
-  __nv_bfloat16* o1 = out + (size_t)(r_begin + tile * PF_BM + lr1) * out_ld + h * HD;
+  float i0 = 1.f / l0, i1 = 1.f / l1;
+  if (sinks) {       // the sink joins the denominator only: with the larger of the two as the reference
+    const float sk = sinks[h] * 1.4426950408889634f;
+    const float mm0 = fmaxf(m0, sk), mm1 = fmaxf(m1, sk), k0 = exp2f(m0 - mm0), k1 = exp2f(m1 - mm1);
+    i0 = k0 / fmaf(l0, k0, exp2f(sk - mm0));
+    i1 = k1 / fmaf(l1, k1, exp2f(sk - mm1));
+  }
+  __nv_bfloat16* o0 = out + (size_t)(r_begin + tile * PF_BM + lr0) * out_ld + h * hdv;
+  __nv_bfloat16* o1 = out + (size_t)(r_begin + tile * PF_BM + lr1) * out_ld + h * hdv;
 #pragma unroll
   for (int d = 0; d < DT; ++d) {
+    if (d * 8 >= hdv) break;
     if (lr0 < rows_here) *reinterpret_cast<uint32_t*>(o0 + d * 8 + 2 * t) = pack_bf16(o[d][0] * i0, o[d][1] * i0);
     if (lr1 < rows_here) *reinterpret_cast<uint32_t*>(o1 + d * 8 + 2 * t) = pack_bf16(o[d][2] * i1, o[d][3] * i1);
   }
@@ -261,8 +289,15 @@ CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc,
                                         const int* seg_start, void* out, int out_ld, int seg0, int n_seg,
                                         int max_seg_rows, int n_head, int n_kv_head, int hd, int ps, float scale,
                                         int window, int n_chunks, int chunk_keys, float* partial, const int* positions,
-                                        int row0, int n_rows, void* stream) {
+                                        int row0, int n_rows, void* stream, int hd_v, int v_row,
+                                        const float* slopes, const float* sinks, float temp_coef, int temp_every) {
   if (n_seg <= 0 || max_seg_rows <= 0) return CBIS_OK;
+  // hd: the keys' width; hd_v (0: the keys'): the values'; both multiples of 8, the wider of them rounded up to a
+  // multiple of 16 picks the tile
+  const int hdk = hd;
+  if (hd_v <= 0) hd_v = hd, v_row = hd;
+  if (hdk % 8 || hd_v % 8 || v_row < hd_v || v_row % 8) return CBIS_ERR_BAD_SIZE;
+  hd = ((hdk > hd_v ? hdk : hd_v) + 15) / 16 * 16;
   if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || chunk_keys % PF_BN || !partial || !positions || n_rows <= 0 ||
                                         ((uintptr_t)partial & 15) || out_ld % 4 || ((uintptr_t)out & 7))))
     return CBIS_ERR_BAD_SIZE;
@@ -287,12 +322,13 @@ CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc,
     }                                                                                                                 \
     e = launch_pdl(kern, grid, dim3(PF_WARPS * 32), smem, st, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, \
                    (const __nv_bfloat16*)vc, block_table, max_blocks, cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, \
-                   n_head, n_kv_head, ps_shift, scale_log2e, window, n_chunks, chunk_keys, partial, row0);            \
+                   n_head, n_kv_head, ps_shift, scale_log2e, window, n_chunks, chunk_keys, partial, row0, hdk, hd_v,  \
+                   v_row, slopes, sinks, temp_coef, temp_every);                                                      \
   }
   CBIS_PF(16) CBIS_PF(32) CBIS_PF(48) CBIS_PF(64) CBIS_PF(80) CBIS_PF(96) CBIS_PF(112) CBIS_PF(128)
 #undef CBIS_PF
   if (e == cudaSuccess && n_chunks > 1)
     e = launch_pdl(prefill_merge_kernel<__nv_bfloat16, true>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions,
-                   (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd, window, n_chunks, chunk_keys, (const float*)nullptr);
+                   (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd_v, window, n_chunks, chunk_keys, sinks);
   return (int)e;
 }

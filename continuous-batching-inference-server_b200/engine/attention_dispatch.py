@@ -50,14 +50,29 @@ def _general_chunks(ctx, mixer, rows, hd):
 
 def _extended(ctx, mixer, qkv, cache, view, out, k_pages, v_pages, k_off, v_off, vd, slopes, sinks, q_temp) -> int:
     """Attention with values of their own width, a distance bias, a sink or a query temperature: the cache-write
-    kernel, then the general kernel over all rows (both precisions, any sizes)."""
-    T, hd, ps = ctx.n_rows, mixer.head_dim, cache.page_size
+    kernel; then, bfloat16 with widths that are multiples of 8 up to 128 and pages of a power of two, the tiled
+    tensor-core kernel for the longer segments and the general kernel for the decoding rows; else the general kernel
+    over all rows (both precisions, any sizes)."""
+    T, nd, hd, ps = ctx.n_rows, ctx.n_decode, mixer.head_dim, cache.page_size
     if mixer.own_kv:
         ops.kv_write(qkv, k_off, v_off, k_pages, v_pages, view.slot_mapping, mixer.n_kv_head, hd, ps, v_head_dim=vd)
-    chunks, partial = _general_chunks(ctx, mixer, T, vd)
-    ops.paged_attention_generic(qkv[:, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq, ctx.positions,
-                                out[:, :mixer.n_head * vd], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
-                                mixer.window, chunks, partial, v_head_dim=vd, slopes=slopes, sinks=sinks, q_temp=q_temp)
+    extra = dict(v_head_dim=vd, slopes=slopes, sinks=sinks, q_temp=q_temp)
+    o = out[:, :mixer.n_head * vd]
+    tiled = (qkv.dtype == torch.bfloat16 and ps & (ps - 1) == 0 and hd % 8 == 0 and vd % 8 == 0 and max(hd, vd) <= 128
+             and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and o.stride(0) % 2 == 0 and ctx.n_segments > nd
+             and ops.USE_TILED_EXTENDED)
+    general_rows = nd if tiled else T
+    if general_rows > 0:
+        r = slice(0, general_rows)
+        chunks, partial = _general_chunks(ctx, mixer, general_rows, vd)
+        ops.paged_attention_generic(qkv[r, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq[r],
+                                    ctx.positions[r], o[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
+                                    mixer.window, chunks, partial, **extra)
+    if tiled:
+        chunks, partial = _key_chunks(ctx, mixer, nd, T, vd)
+        ops.paged_prefill_bf16(qkv, k_pages, v_pages, view.block_table, ctx.cu_rows, ctx.seg_start, o, nd,
+                               ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
+                               mixer.window, chunks, partial, ctx.positions, nd, T - nd, **extra)
     return vd
 
 

@@ -293,6 +293,7 @@ def gemm_few_rows(x, w_nk, bias, act, out, ksplit=0):
 
 _tc_error = {}
 USE_TCGEN05 = __import__("os").environ.get("CBIS_TCGEN05", "1") != "0"
+USE_TILED_EXTENDED = __import__("os").environ.get("CBIS_TILED_EXTENDED", "1") != "0"   # 0: attention with a bias, a sink or values of their own width goes to the general kernel for prompts too
 USE_KEY_CHUNKS = __import__("os").environ.get("CBIS_KEY_CHUNKS", "1") != "0"   # 0: attention kernels never cut the keys over more blocks
 USE_TILED_F32 = __import__("os").environ.get("CBIS_TILED_F32", "1") != "0"   # 0: the general kernel for 32-bit prompts
 USE_FEW_ROWS = USE_TCGEN05 and __import__("os").environ.get("CBIS_FEW_ROWS", "1") != "0"
@@ -586,29 +587,39 @@ def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq,
 
 def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
                        n_head, n_kv_head, head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None,
-                       positions=None, row0=0, n_rows=0):
+                       positions=None, row0=0, n_rows=0, v_head_dim=0, slopes=None, sinks=None, q_temp=None):
     """Attention of the segments seg0..seg0+n_seg-1 (runs of rows given by ``cu_rows``, first positions
     ``seg_start``) over their pages, on the tensor cores.  Head sizes 16, 32, ... 128, page sizes 2^k.
+    With ``v_head_dim`` keys and values may have different widths, multiples of 8 up to 128 (the value pages may be
+    the key pages: a row's first entries are then its values); ``slopes``, ``sinks``, ``q_temp``: as in
+    ``paged_attention_generic``.
     ``chunks`` = (n, keys) from ``prefill_key_chunks`` cuts the keys n ways over more blocks (every context of the
     step below n * keys); ``partial`` then holds ``n_rows * n_head * n * (head_dim + 4)`` floats, ``positions`` the
     position of every row, ``row0`` and ``n_rows`` name the rows of these segments."""
     _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, partial, positions)
-    if head_dim % 16 or not 16 <= head_dim <= 128:
+    vd = int(v_head_dim) or head_dim
+    if not v_head_dim and (head_dim % 16 or not 16 <= head_dim <= 128):
         raise KernelError(f"prefill attention: head_dim={head_dim} is no multiple of 16 up to 128 (the general kernel takes it)")
+    if head_dim % 8 or vd % 8 or not 8 <= max(head_dim, vd) <= 128:
+        raise KernelError(f"prefill attention: widths {head_dim} and {vd} are no multiples of 8 up to 128 (the general kernel takes them)")
     if page_size & (page_size - 1):
         raise KernelError(f"prefill attention: page_size={page_size} is not a power of two (the general kernel takes it)")
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.is_contiguous()
+    v_row = v_cache.shape[-1]
+    for t in (slopes, sinks):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n_head and t.is_cuda)
+    coef, every = q_temp if q_temp else (0.0, 0)
     n_chunks, chunk_keys = chunks
     if n_chunks > 1:
-        assert partial.dtype == torch.float32 and partial.numel() >= n_rows * n_head * n_chunks * (head_dim + 4)
+        assert partial.dtype == torch.float32 and partial.numel() >= n_rows * n_head * n_chunks * (vd + 4)
         assert positions.dtype == torch.int32 and positions.numel() >= row0 + n_rows
     st = kernels().cbis_paged_prefill_bf16(
         _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(cu_rows), _ptr(seg_start), _ptr(out), c_int(out.stride(0)), c_int(seg0), c_int(n_seg),
         c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim), c_int(page_size), c_float(scale),
         c_int(window), c_int(n_chunks), c_int(chunk_keys), _ptr(partial), _ptr(positions), c_int(row0), c_int(n_rows),
-        _stream())
+        _stream(), c_int(vd), c_int(v_row), _ptr(slopes), _ptr(sinks), c_float(coef), c_int(int(every)))
     _check(st, "paged_prefill_bf16", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size} "
                                      f"chunks={n_chunks}x{chunk_keys}")
 
