@@ -721,7 +721,7 @@ def figotar_kernels(torch, ops, pk):
             st = torch.zeros(segs, ops.matrix_memory_state_floats(H, D, V), device="cuda")
             y = torch.empty(rows, H * V, device="cuda")
             return lambda: ops.matrix_memory(qkv, 0, H * D, 2 * H * D, gates, ib, fb, 15.0, D ** -0.5, 1e-6, st, seg_slot, cu,
-                                             segs, H, D, V, y)
+                                             segs, H, D, V, y, max_seg_rows=per)
         timed(memory, rows * ((2 * H * D + H * V) * 2 + H * V * 4) + 2 * segs * H * D * V * 4, f"matrix_memory_{tag}")
 
         def scan():
@@ -786,7 +786,18 @@ def figotar_kernels(torch, ops, pk):
         part = torch.empty(B * nh * max(1, chunks[0]) * (hd + 4), device="cuda")
         return lambda: ops.paged_attention_generic(q, k, v, btB, row_seq, pos, o, nh, nkv, hd, ps, hd ** -0.5, 1024, chunks, part,
                                                    v_head_dim=hd, slopes=slopes, q_temp=(0.1, 512))
-    timed(decode_general, B * 1024 * 2 * nkv * hd * 2, "attention_decode_8_bias_temperature")
+    timed(decode_general, B * 1024 * 2 * nkv * hd * 2, "attention_decode_8_bias_temperature_general_kernel")
+
+    def decode_lanes():          # what the engine runs: the decode kernel's lane-group form, keys split over blocks
+        qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda").to(bf)
+        k, v = (torch.randn(B * pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+        o = torch.empty(B, nh * hd, dtype=bf, device="cuda")
+        ns = ops.decode_splits(B, nh, ctx_len)
+        scratch = torch.empty(max(1, ops.decode_scratch_floats(B, nh, hd, ns)), device="cuda")
+        counters = torch.zeros(B * nh, dtype=torch.int32, device="cuda")
+        return lambda: ops.paged_decode_bf16(qkv, nh * hd, (nh + nkv) * hd, k, v, btB, row_seq, pos, slot_map, o, scratch, counters,
+                                             nh, nkv, hd, ps, hd ** -0.5, 1024, ns, v_head_dim=hd, slopes=slopes, q_temp=(0.1, 512))
+    timed(decode_lanes, B * 1024 * 2 * nkv * hd * 2, "attention_decode_8_bias_temperature")
 
     def decode_plain():
         qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda").to(bf)

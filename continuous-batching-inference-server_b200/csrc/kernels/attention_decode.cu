@@ -13,6 +13,11 @@
 // The current token's key and value can come straight from the step's projections (`k_off >= 0`):
 // the block that meets position p takes them from `qkv` and stores them into the page, so the
 // separate cache-write launch is not needed at decode.
+//
+// The lane-group form also takes values of another width than the keys (hdv; lane i of a group holds entries
+// 8i .. 8i+7 of both), values that are the first entries of the keys' rows (vc == kc, v_row: elements between two
+// tokens' values), a distance bias (slope[h] * (p - j) taken off the score), a query temperature by position and a
+// sink in the denominator.
 #include "attention_decode_tc.cuh"
 #include <math.h>
 
@@ -29,7 +34,8 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
                          const int* positions, const int* slot_mapping,
                          __nv_bfloat16* __restrict__ out, int out_ld, float* part,
                          unsigned int* counters, int n_head, int n_kv_head, int hd, int ps, float scale,
-                         int window, int nsplit) {
+                         int window, int nsplit, int hdv, int v_row, const float* __restrict__ slopes,
+                         const float* __restrict__ sinks, float temp_coef, int temp_every) {
   constexpr int G = 32 / LPK;             // key groups per warp
   constexpr int NW = DEC_WARPS * G;       // key workers per block
   __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
@@ -42,7 +48,7 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
   const int seq = row_seq[row];
   if (seq < 0) {  // a padding row of a fixed-size batch
     if (split == 0)
-      for (int t = threadIdx.x; t < hd; t += blockDim.x) out[(size_t)row * out_ld + h * hd + t] = __float2bfloat16_rn(0.f);
+      for (int t = threadIdx.x; t < hdv; t += blockDim.x) out[(size_t)row * out_ld + h * hdv + t] = __float2bfloat16_rn(0.f);
     return;
   }
   const int hk = h / (n_head / n_kv_head);
@@ -53,9 +59,11 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
   const int ks = kstart + split * per;
   const int ke = min(kend, ks + per);
   const int sub = lane % LPK, group = lane / LPK;
-  const bool active = sub * 8 < hd;
+  const bool active = sub * 8 < hd, active_v = sub * 8 < hdv;
   const int* bt = block_table + (size_t)seq * max_blocks;
   const bool fused = k_off >= 0;
+  if (temp_every > 0) scale *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+  const float slope = slopes ? slopes[h] : 0.f;
 
   float q[8];
   {
@@ -78,21 +86,21 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
       const int j = base + u * NW + wkr;
       kk[u] = make_uint4(0, 0, 0, 0);
       vv[u] = make_uint4(0, 0, 0, 0);
-      if (j < ke && active) {
+      if (j < ke && (active || active_v)) {
         if (fused && j == pos) {
-          kk[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + k_off + hk * hd + sub * 8);
-          vv[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + v_off + hk * hd + sub * 8);
+          if (active) kk[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + k_off + hk * hd + sub * 8);
+          if (active_v) vv[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + v_off + hk * hdv + sub * 8);
           const int slot = slot_mapping[row];
           if (slot >= 0) {
-            const size_t dst = (((size_t)(slot / ps) * n_kv_head + hk) * ps + (slot % ps)) * hd + sub * 8;
-            *reinterpret_cast<uint4*>(kc + dst) = kk[u];
-            *reinterpret_cast<uint4*>(vc + dst) = vv[u];
+            const size_t token = ((size_t)(slot / ps) * n_kv_head + hk) * ps + (slot % ps);
+            if (active) *reinterpret_cast<uint4*>(kc + token * hd + sub * 8) = kk[u];
+            if (active_v && vc != kc) *reinterpret_cast<uint4*>(vc + token * v_row + sub * 8) = vv[u];
           }
         } else {
           const int page = bt[j / ps];
-          const size_t src = (((size_t)page * n_kv_head + hk) * ps + (j % ps)) * hd + sub * 8;
-          kk[u] = *reinterpret_cast<const uint4*>(kc + src);
-          vv[u] = *reinterpret_cast<const uint4*>(vc + src);
+          const size_t token = ((size_t)page * n_kv_head + hk) * ps + (j % ps);
+          if (active) kk[u] = *reinterpret_cast<const uint4*>(kc + token * hd + sub * 8);
+          if (active_v) vv[u] = *reinterpret_cast<const uint4*>(vc + token * v_row + sub * 8);
         }
       }
     }
@@ -118,7 +126,7 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
       for (int i = 0; i < 8; ++i) d = fmaf(q[i], kf[i], d);
 #pragma unroll
       for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      s[u] = valid[u] ? d : -INFINITY;
+      s[u] = valid[u] ? d - slope * (float)(pos - (base + u * NW + wkr)) : -INFINITY;
     }
     float m_new = m;
 #pragma unroll
@@ -164,7 +172,7 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
     sm_m[warp] = m;
     sm_l[warp] = l;
   }
-  if (group == 0 && active) {
+  if (group == 0 && active_v) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) sm_acc[warp][sub * 8 + i] = acc[i];
   }
@@ -178,18 +186,25 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
     wgt[w] = sm_m[w] > -INFINITY ? expf(sm_m[w] - M) : 0.f;
     L += sm_l[w] * wgt[w];
   }
-  for (int t = threadIdx.x; t < hd; t += blockDim.x) {
+  // the sink joins the denominator only: with the larger of the two as the reference
+  float keep1 = 1.f;
+  if (sinks && nsplit == 1) {
+    const float sk = sinks[h], mm = fmaxf(M, sk);
+    keep1 = expf(M - mm);
+    L = fmaf(L, keep1, expf(sk - mm));
+  }
+  for (int t = threadIdx.x; t < hdv; t += blockDim.x) {
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) v += sm_acc[w][t] * wgt[w];
     if (nsplit == 1) {
-      out[(size_t)row * out_ld + h * hd + t] = __float2bfloat16_rn(v / L);
+      out[(size_t)row * out_ld + h * hdv + t] = __float2bfloat16_rn(v * keep1 / L);
     } else {
-      float* p = part + (((size_t)row * n_head + h) * nsplit + split) * (hd + 2);
+      float* p = part + (((size_t)row * n_head + h) * nsplit + split) * (hdv + 2);
       p[t] = v;
       if (t == 0) {
-        p[hd] = M;
-        p[hd + 1] = L;
+        p[hdv] = M;
+        p[hdv + 1] = L;
       }
     }
   }
@@ -201,19 +216,19 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  const float* p = part + ((size_t)row * n_head + h) * nsplit * (hd + 2);
-  float Mx = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) Mx = fmaxf(Mx, __ldcg(p + (size_t)s * (hd + 2) + hd));
-  for (int t = threadIdx.x; t < hd; t += blockDim.x) {
-    float Ls = 0.f, v = 0.f;
+  const float* p = part + ((size_t)row * n_head + h) * nsplit * (hdv + 2);
+  float Mx = sinks ? sinks[h] : -INFINITY;
+  for (int s = 0; s < nsplit; ++s) Mx = fmaxf(Mx, __ldcg(p + (size_t)s * (hdv + 2) + hdv));
+  for (int t = threadIdx.x; t < hdv; t += blockDim.x) {
+    float Ls = sinks ? expf(sinks[h] - Mx) : 0.f, v = 0.f;
     for (int s = 0; s < nsplit; ++s) {
-      const float* ps_ = p + (size_t)s * (hd + 2);
-      const float ms = __ldcg(ps_ + hd);
+      const float* ps_ = p + (size_t)s * (hdv + 2);
+      const float ms = __ldcg(ps_ + hdv);
       const float w = ms > -INFINITY ? expf(ms - Mx) : 0.f;
-      Ls += __ldcg(ps_ + hd + 1) * w;
+      Ls += __ldcg(ps_ + hdv + 1) * w;
       v += __ldcg(ps_ + t) * w;
     }
-    out[(size_t)row * out_ld + h * hd + t] = __float2bfloat16_rn(v / Ls);
+    out[(size_t)row * out_ld + h * hdv + t] = __float2bfloat16_rn(v / Ls);
   }
   if (threadIdx.x == 0) counters[row * n_head + h] = 0;
 }
@@ -286,8 +301,15 @@ CBIS_EXPORT int cbis_paged_decode_bf16(const void* qkv, int ld, int k_off, int v
                                        const int* block_table, int max_blocks, const int* row_seq,
                                        const int* positions, const int* slot_mapping, void* out, int out_ld,
                                        float* part, unsigned int* counters, int rows, int n_head, int n_kv_head,
-                                       int hd, int ps, float scale, int window, int nsplit, void* stream) {
+                                       int hd, int ps, float scale, int window, int nsplit, void* stream, int hdv,
+                                       int v_row, const float* slopes, const float* sinks, float temp_coef,
+                                       int temp_every) {
   if (rows <= 0) return CBIS_OK;
+  // hdv (0: the keys' width, values in pages of their own): the values' width; with it, a bias, a sink or a
+  // temperature the lane-group form runs whatever the head size
+  const bool extended = hdv > 0 || slopes || sinks || temp_every > 0;
+  if (hdv <= 0) hdv = hd, v_row = hd;
+  if (hdv > 256 || hdv % 8 || v_row < hdv || v_row % 8) return CBIS_ERR_BAD_SIZE;
   if (hd <= 0 || hd > 256 || hd % 8 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head || nsplit < 1 || nsplit > 32)
     return CBIS_ERR_BAD_SIZE;
   if (ld % 8 || out_ld % 8 || (k_off >= 0 && (k_off % 8 || v_off % 8)) || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) ||
@@ -296,9 +318,9 @@ CBIS_EXPORT int cbis_paged_decode_bf16(const void* qkv, int ld, int k_off, int v
   if (nsplit > 1 && (part == nullptr || counters == nullptr)) return CBIS_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(rows, n_head, nsplit);
-  const int chunks = hd / 8;
+  const int chunks = (hd > hdv ? hd : hdv) / 8;
   cudaError_t e;
-  if ((hd == 64 || hd == 128) && ps % 16 == 0) {
+  if ((hd == 64 || hd == 128) && ps % 16 == 0 && !extended) {
     if (hd == 128)
       e = launch_pdl(paged_decode_tc_kernel<128>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)qkv, ld, k_off,
                      v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, max_blocks, row_seq, positions,
@@ -315,7 +337,7 @@ CBIS_EXPORT int cbis_paged_decode_bf16(const void* qkv, int ld, int k_off, int v
   e = launch_pdl(paged_decode_bf16_kernel<LPK>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)qkv, ld, \
                  k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, max_blocks, row_seq, positions, \
                  slot_mapping, (__nv_bfloat16*)out, out_ld, part, counters, n_head, n_kv_head, hd, ps, scale, window, \
-                 nsplit)
+                 nsplit, hdv, v_row, slopes, sinks, temp_coef, temp_every)
   if (chunks <= 2) CBIS_DEC(2);
   else if (chunks <= 4) CBIS_DEC(4);
   else if (chunks <= 8) CBIS_DEC(8);

@@ -49,30 +49,42 @@ def _general_chunks(ctx, mixer, rows, hd):
 
 
 def _extended(ctx, mixer, qkv, cache, view, out, k_pages, v_pages, k_off, v_off, vd, slopes, sinks, q_temp) -> int:
-    """Attention with values of their own width, a distance bias, a sink or a query temperature: the cache-write
-    kernel; then, bfloat16 with widths that are multiples of 8 up to 128 and pages of a power of two, the tiled
-    tensor-core kernel for the longer segments and the general kernel for the decoding rows; else the general kernel
-    over all rows (both precisions, any sizes)."""
+    """Attention with values of their own width, a distance bias, a sink or a query temperature.  bfloat16 with
+    widths that are multiples of 8: the decoding rows go to the split-KV decode kernel's lane-group form (up to 256
+    wide; it stores the current token's key and value itself), the longer segments, after the cache-write kernel, to
+    the tiled tensor-core kernel (up to 128 wide, pages of a power of two).  32-bit, other sizes: the cache-write
+    kernel and the general kernel."""
     T, nd, hd, ps = ctx.n_rows, ctx.n_decode, mixer.head_dim, cache.page_size
-    if mixer.own_kv:
-        ops.kv_write(qkv, k_off, v_off, k_pages, v_pages, view.slot_mapping, mixer.n_kv_head, hd, ps, v_head_dim=vd)
     extra = dict(v_head_dim=vd, slopes=slopes, sinks=sinks, q_temp=q_temp)
     o = out[:, :mixer.n_head * vd]
-    tiled = (qkv.dtype == torch.bfloat16 and ps & (ps - 1) == 0 and hd % 8 == 0 and vd % 8 == 0 and max(hd, vd) <= 128
-             and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and o.stride(0) % 2 == 0 and ctx.n_segments > nd
-             and ops.USE_TILED_EXTENDED)
-    general_rows = nd if tiled else T
-    if general_rows > 0:
-        r = slice(0, general_rows)
-        chunks, partial = _general_chunks(ctx, mixer, general_rows, vd)
-        ops.paged_attention_generic(qkv[r, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq[r],
-                                    ctx.positions[r], o[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
-                                    mixer.window, chunks, partial, **extra)
-    if tiled:
-        chunks, partial = _key_chunks(ctx, mixer, nd, T, vd)
-        ops.paged_prefill_bf16(qkv, k_pages, v_pages, view.block_table, ctx.cu_rows, ctx.seg_start, o, nd,
-                               ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
-                               mixer.window, chunks, partial, ctx.positions, nd, T - nd, **extra)
+    by8 = (qkv.dtype == torch.bfloat16 and hd % 8 == 0 and vd % 8 == 0 and qkv.stride(0) % 8 == 0 and k_off % 8 == 0
+           and v_off % 8 == 0 and qkv.data_ptr() % 16 == 0 and o.stride(0) % 8 == 0 and o.data_ptr() % 16 == 0)
+    fast_decode = by8 and nd > 0 and max(hd, vd) <= 256
+    tiled = by8 and T > nd and max(hd, vd) <= 128 and ps & (ps - 1) == 0 and ops.USE_TILED_EXTENDED
+    first = nd if fast_decode else 0        # rows from here on have their keys and values stored by the cache-write kernel
+    if fast_decode:
+        nsplit = ops.decode_splits(nd, mixer.n_head, ctx.ctx_limit)
+        scratch = counters = None
+        if nsplit > 1:
+            scratch, counters = ctx.decode_scratch(ops.decode_scratch_floats(nd, mixer.n_head, vd, nsplit), nd * mixer.n_head)
+        ops.paged_decode_bf16(qkv[:nd], k_off if mixer.own_kv else -1, v_off if mixer.own_kv else -1, k_pages, v_pages,
+                              view.block_table, ctx.row_seq, ctx.positions, view.slot_mapping, o[:nd], scratch, counters,
+                              mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale, mixer.window, nsplit, **extra)
+    if first >= T:
+        return vd
+    r = slice(first, T)
+    if mixer.own_kv:
+        ops.kv_write(qkv[r], k_off, v_off, k_pages, v_pages, view.slot_mapping[r], mixer.n_kv_head, hd, ps, v_head_dim=vd)
+    if tiled:        # q and out keep their full row numbering, the kernel finds its rows through cu_rows
+        chunks, partial = _key_chunks(ctx, mixer, first, T, vd)
+        ops.paged_prefill_bf16(qkv, k_pages, v_pages, view.block_table, ctx.cu_rows, ctx.seg_start, o, first,
+                               ctx.n_segments - first, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
+                               mixer.window, chunks, partial, ctx.positions, first, T - first, **extra)
+        return vd
+    chunks, partial = _general_chunks(ctx, mixer, T - first, vd)
+    ops.paged_attention_generic(qkv[r, :mixer.d_q], k_pages, v_pages, view.block_table, ctx.row_seq[r], ctx.positions[r],
+                                o[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale, mixer.window, chunks, partial,
+                                **extra)
     return vd
 
 

@@ -564,24 +564,31 @@ def decode_scratch_floats(rows: int, n_head: int, head_dim: int, nsplit: int) ->
 
 
 def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out,
-                      scratch, counters, n_head, n_kv_head, head_dim, page_size, scale, window, nsplit):
+                      scratch, counters, n_head, n_kv_head, head_dim, page_size, scale, window, nsplit, v_head_dim=0,
+                      slopes=None, sinks=None, q_temp=None):
     """Decode attention (one query per row) with the keys split ``nsplit`` ways; with ``k_off >= 0`` the
     current token's key/value are taken from ``qkv`` and stored into the cache by the same kernel.
     ``scratch``: ``decode_scratch_floats`` floats; ``counters``: rows*n_head int32, zero before the
-    first launch (every launch leaves them zero)."""
-    _need_cuda(qkv, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out, scratch, counters)
+    first launch (every launch leaves them zero).  ``v_head_dim``, ``slopes``, ``sinks``, ``q_temp``: as in
+    ``paged_attention_generic`` (widths multiples of 8 up to 256; the scratch is then sized by the values' width)."""
+    _need_cuda(qkv, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out, scratch, counters, slopes, sinks)
     rows = qkv.shape[0]
-    if head_dim % 8 or head_dim > 256:
-        raise KernelError(f"decode attention: head_dim={head_dim} must be a multiple of 8, at most 256")
+    vd = int(v_head_dim) or head_dim
+    if head_dim % 8 or head_dim > 256 or vd % 8 or vd > 256:
+        raise KernelError(f"decode attention: widths {head_dim} and {vd} must be multiples of 8, at most 256")
     assert qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    for t in (slopes, sinks):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n_head)
+    coef, every = q_temp if q_temp else (0.0, 0)
     if nsplit > 1:
-        assert scratch.dtype == torch.float32 and scratch.numel() >= decode_scratch_floats(rows, n_head, head_dim, nsplit)
+        assert scratch.dtype == torch.float32 and scratch.numel() >= decode_scratch_floats(rows, n_head, vd, nsplit)
         assert counters.dtype == torch.int32 and counters.numel() >= rows * n_head
     st = kernels().cbis_paged_decode_bf16(
         _ptr(qkv), c_int(qkv.stride(0)), c_int(k_off), c_int(v_off), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
         c_int(block_table.shape[1]), _ptr(row_seq), _ptr(positions), _ptr(slot_mapping), _ptr(out),
         c_int(out.stride(0)), _ptr(scratch), _ptr(counters), c_int(rows), c_int(n_head), c_int(n_kv_head),
-        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(nsplit), _stream())
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(nsplit), _stream(),
+        c_int(int(v_head_dim)), c_int(v_cache.shape[-1]), _ptr(slopes), _ptr(sinks), c_float(coef), c_int(int(every)))
     _check(st, "paged_decode_bf16", f"rows={rows} heads={n_head}/{n_kv_head} head_dim={head_dim} splits={nsplit}")
 
 
@@ -885,13 +892,14 @@ def matrix_memory_state_floats(heads: int, dim: int, v_dim: int) -> int:
 
 
 def matrix_memory(qkv, q_off, k_off, v_off, gates, i_bias, f_bias, cap, q_scale, den_eps, state, seg_slot, cu_rows,
-                  n_segments, heads, dim, v_dim, y):
+                  n_segments, heads, dim, v_dim, y, max_seg_rows: int = 0):
     """The recurrence of a matrix memory with exponential gates over every segment's rows, from and into the requests'
     states: per head m' = max(lf + m, li), S <- exp(lf + m - m') S + exp(li - m') k v^T, n likewise with k alone,
     y = S^T q / (max(|n . q|, exp(-m')) + den_eps), with li = cap tanh((i + i_bias) / cap) and
     lf = logsigmoid(cap tanh((f + f_bias) / cap)).  ``qkv``: the compute type, q | k | v at their column offsets
     (q is multiplied by ``q_scale``); ``gates``: 32-bit ``[T, 2 * heads]``, raw input gates then raw forget gates;
-    ``y``: 32-bit ``[T, heads * v_dim]``; ``state``: 32-bit ``[slots, matrix_memory_state_floats]``."""
+    ``y``: 32-bit ``[T, heads * v_dim]``; ``state``: 32-bit ``[slots, matrix_memory_state_floats]``;
+    ``max_seg_rows``: the step's longest segment if known (a step of short segments takes smaller batches of rows)."""
     _need_cuda(qkv, gates, i_bias, f_bias, state, seg_slot, cu_rows, y)
     T = qkv.shape[0]
     assert qkv.stride(1) == 1 and gates.dtype == torch.float32 and gates.stride(1) == 1 and gates.shape == (T, 2 * heads)
@@ -902,7 +910,7 @@ def matrix_memory(qkv, q_off, k_off, v_off, gates, i_bias, f_bias, cap, q_scale,
                                       c_int(gates.stride(0)), _ptr(i_bias), _ptr(f_bias), c_float(cap), c_float(q_scale),
                                       c_float(den_eps), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(seg_slot),
                                       _ptr(cu_rows), _ptr(y), c_int(y.stride(0)), c_int(n_segments), c_int(heads), c_int(dim),
-                                      c_int(v_dim), c_int(dtype_code(qkv.dtype)), _stream())
+                                      c_int(v_dim), c_int(dtype_code(qkv.dtype)), _stream(), c_int(int(max_seg_rows)))
     _check(st, "matrix_memory", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim}")
 
 

@@ -66,7 +66,8 @@ class MatrixMemoryMixer(Mixer):
         gates = ops.linear(h, self.w_gates, None, None, out_dtype=torch.float32)         # raw input | forget gates
         y = torch.empty((T, self.d_v), dtype=torch.float32, device=h.device)
         ops.matrix_memory(proj, 0, self.d_qk, 2 * self.d_qk, gates, self.i_bias, self.f_bias, self.gate_cap, self.q_scale,
-                          self.den_eps, state, ctx.seg_slot, ctx.cu_rows, ctx.n_segments, self.heads, self.dim, self.v_dim, y)
+                          self.den_eps, state, ctx.seg_slot, ctx.cu_rows, ctx.n_segments, self.heads, self.dim, self.v_dim, y,
+                          max_seg_rows=ctx.max_seg_rows)
         g = torch.empty((T, self.d_v), dtype=h.dtype, device=h.device)
         g0 = 2 * self.d_qk + self.d_v
         ops.rms_norm(y, self.norm_w, self.eps, g, parts=self.heads, gate=proj[:, g0:g0 + self.d_v], gate_act="sigmoid",

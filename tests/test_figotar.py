@@ -30,14 +30,14 @@ def rounded(t, dtype):
 def test_norm_after_a_part_added_and_norm_before_the_next(dtype):
     from cbis_b200.kernels import ops
     g = torch.Generator().manual_seed(1)
-    for width in (40, 321, 4096):
+    for width, pad in ((40, 3), (40, 4), (321, 3), (1000, 8), (4096, 4), (4100, 4)):     # rows in registers, or staged
         x = torch.randn(9, width, generator=g) * 2
-        y = rounded(torch.randn(9, width + 3, generator=g) * 5, dtype)
+        y = rounded(torch.randn(9, width + pad, generator=g) * 5, dtype)
         bias, wb, w = (0.3 * torch.randn(width, generator=g) for _ in range(3))
-        xd, yd = x.cuda(), dev(y.float(), dtype)[:, 3:]
+        xd, yd = x.cuda(), dev(y.float(), dtype)[:, pad:]
         out = torch.empty(9, width, dtype=DTYPES[dtype], device="cuda")
         ops.add_rmsnorm(xd, yd, bias.cuda(), (wb.cuda(), 1e-3, 1.0), w.cuda(), 1e-4, 1.0, out)
-        d = pf.rms_norm((y[:, 3:] + bias.double()).numpy(), wb.numpy(), 1e-3, 1.0)
+        d = pf.rms_norm((y[:, pad:] + bias.double()).numpy(), wb.numpy(), 1e-3, 1.0)
         x_ref = x.double().numpy() + d
         ref = pf.rms_norm(x_ref, w.numpy(), 1e-4, 1.0)
         assert np.abs(xd.double().cpu().numpy() - x_ref).max() < 1e-5 * np.abs(x_ref).max()     # the stream stays 32-bit
@@ -133,7 +133,8 @@ def test_matrix_memory_recurrence_over_steps(H, D, V, dtype):
             y = torch.empty(len(rows), H * V, dtype=torch.float32, device="cuda")
             ops.matrix_memory(dev(qkv[idx].float(), dtype), 3, 3 + H * D, 3 + 2 * H * D, gates[idx].cuda().contiguous(),
                               ib.cuda(), fb.cuda(), cap, qs, 1e-6, state, torch.tensor(slots, dtype=torch.int32, device="cuda"),
-                              torch.tensor(cu, dtype=torch.int32, device="cuda"), len(slots), H, D, V, y)
+                              torch.tensor(cu, dtype=torch.int32, device="cuda"), len(slots), H, D, V, y,
+                              max_seg_rows=max(n for _, n in step))        # steps of short segments take another form
             y_all[idx] = y.double().cpu()
         assert fed == lens
         return y_all
@@ -198,6 +199,18 @@ def test_attention_kernels_with_bias_temperature_sink_and_unlike_widths(dtype):
                                    out2, 0, 2, max(lens), H, G, D, ps, scale, window, v_head_dim=V, slopes=sl, sinks=sk,
                                    q_temp=temp)
             assert (out2.double().cpu() - ref).abs().max() < tol, (D, V, shared, "tiled")
+            # the decode kernel on each request's last row, its keys whole and split three ways
+            last = torch.tensor([lens[0] - 1, T - 1])
+            qd = dev(q[last].float(), dtype)
+            rs = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+            ps_ = torch.tensor([lens[0] - 1, lens[1] - 1], dtype=torch.int32, device="cuda")
+            for nsplit in (1, 3):
+                out3 = torch.zeros(2, H * V, dtype=DTYPES[dtype], device="cuda")
+                scratch = torch.empty(max(1, ops.decode_scratch_floats(2, H, V, nsplit)), device="cuda")
+                counters = torch.zeros(2 * H, dtype=torch.int32, device="cuda")
+                ops.paged_decode_bf16(qd, -1, -1, kd, vd, bt.cuda(), rs, ps_, ps_, out3, scratch, counters, H, G, D, ps, scale,
+                                      window, nsplit, v_head_dim=V, slopes=sl, sinks=sk, q_temp=temp)
+                assert (out3.double().cpu() - ref[last]).abs().max() < tol, (D, V, shared, "decode", nsplit)
 
 
 # ---- each mechanism as a model of one layer, and the mixed models -------------------------------------------
