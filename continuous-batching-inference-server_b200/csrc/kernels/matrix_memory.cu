@@ -149,6 +149,7 @@ matrix_memory_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, con
     __syncthreads();
     if (first + TC < n_rows) fetch(first + TC);      // in flight while these rows are walked
     if (!carrier) {
+#pragma unroll 4     // rows in flight together: 2 took 860 us for 2,048 rows of 8 heads of 128 x 256, 4 takes 660, 8 takes 760
       for (int t = 0; t < tc; ++t) {
         const float keep = g_keep[t], tv = g_take[t] * vs[t * CB + c];
         const float* kt = ks + t * DP + l;
@@ -166,6 +167,7 @@ matrix_memory_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, con
         if (l == 0) nums[t * CB + c] = acc;
       }
     } else {
+#pragma unroll 4
       for (int t = 0; t < tc; ++t) {
         const float keep = g_keep[t], take = g_take[t];
         const float* kt = ks + t * DP + l;

@@ -253,6 +253,19 @@ def test_sizes_of_the_tiled_kernels(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_widths_beyond_the_tiled_kernels(dtype):
+    """Keys of 160 with values of 136, and a cached row of 160 + 32 entries: wider than the tiled kernel's tiles (the
+    decode kernel takes them up to 256, prompts go to the general kernel)."""
+    cfgd = config(64, 80, [attn(2, 1, 160, 136, 40, 0.08, mlp=dense(32)), latent(2, 32, 32, 32, 160, 48, 0.1, mlp=None)])
+    w = make_weights(cfgd, 19, std=0.12)
+    toks = tokens_of(cfgd, 90, 7)
+    ref = plain(cfgd, w, toks)
+    eng = make_engine(cfgd, w, dtype, page_size=16, num_pages=16)
+    for sizes in ([90], [33, 2, 40, 15], [60] + [1] * 30):
+        assert_close(run_cut(eng, toks, sizes), ref, dtype, sizes)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["mixed", "odd"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(name, dtype):
     """Six requests through three slots and a pool smaller than the requests together: portions of some beside single
