@@ -635,8 +635,8 @@ def figotar_sizes(width, layers):
     heads = width // hd
     att = {"dim": hd, "heads": heads, "kv_heads": max(1, heads // 4), "mask": {"size": 1024 if big else 512},
            "q_temp": {"coef": 0.1, "every": 512}, "scale": hd ** -0.5, "vdim": hd}
-    lat = {"dim": 64, "heads": 16, "kv_rank": 96, "q_rank": width // 4, "rot": {"base": 10000.0, "dims": 32},
-           "rot_dim": 32, "scale": 96 ** -0.5, "vdim": 64}
+    lat = {"dim": 64, "heads": 16, "kv_rank": 64, "q_rank": width // 4, "rot": {"base": 10000.0, "dims": 64},
+           "rot_dim": 64, "scale": 128 ** -0.5, "vdim": 64}
     mem = {"dim": hd, "gate_cap": 15.0, "heads": heads // 2, "vdim": 2 * hd}
     mlp = {"kind": "dense", "ff": 8 * width // 3 // 64 * 64}
     out = []

@@ -56,8 +56,8 @@ ODD = config(40, 61, [
 # sizes that take the tiled kernels: widths in multiples of 8 and 16 up to 128, several cache groups, a window across
 # many pages, memories of 64 and 128 with 48 and 80 columns
 WIDE = config(128, 200, [
-    attn(4, 2, 64, 80, 70, 0.125, q_temp=(0.5, 32), mlp=dense(192)),
-    latent(4, 32, 32, 32, 96, 48, 0.11, base=10000.0, mlp=dense(96)),
+    attn(4, 2, 48, 80, 70, 0.14, q_temp=(0.5, 32), mlp=dense(192)),
+    latent(4, 32, 32, 32, 80, 48, 0.11, base=10000.0, mlp=dense(96)),
     mlstm(2, 64, 48, mlp=dense(128)),
     attn(2, 1, 128, 64, 33, 0.09, q_temp=(0.1, 64), mlp=None),
     latent(2, 64, 16, 64, 48, 80, 0.1, mlp=dense(64)),

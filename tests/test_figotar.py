@@ -154,7 +154,7 @@ def test_attention_kernels_with_bias_temperature_sink_and_unlike_widths(dtype):
     from cbis_b200.kernels import ops
     g = torch.Generator().manual_seed(5)
     ps, H, G = 8, 4, 2
-    for D, V, shared in ((16, 24, False), (40, 24, True), (64, 80, False), (128, 96, True), (12, 20, False)):
+    for D, V, shared in ((16, 24, False), (40, 24, True), (48, 80, False), (128, 104, True), (12, 20, False)):
         lens = [70, 33]
         T = sum(lens)
         q = rounded(torch.randn(T, H * D, generator=g), dtype)
